@@ -1,0 +1,211 @@
+// MoE routing: router logits, softmax over all experts, top-k, and the stable
+// group-by-expert dispatch tables.
+//
+// Reference behaviour: a library GEMM for the logits followed by RouteTopKKernel
+// (src/backends/cuda/ops/moe.cu:36-127): fp32 softmax with max subtraction over
+// all E, k rounds of masked argmax with a strictly-greater compare (ties go to
+// the lower index), optional renormalisation of the k weights (guarded by
+// total > 0), then the routed scale; slots are in descending-probability order.
+// Here the logits are computed in the same kernel in fp32 (the router weight is
+// kept in fp32), and one extra weight row (the shared expert's gate) can ride
+// along since it reads the same activations.
+//
+// Dispatch: CountPerExpert / ScanOffsets / ScatterByExpert (moe.cu:130-221):
+// offsets[E+1], rows[A] (source token of each grouped row) and dest[A] (grouped
+// row of assignment t*k+slot); inside an expert rows ascend by assignment index.
+#include "common.cuh"
+
+#define ROUTER_THREADS 256
+#define ROUTER_MAX_TOK 8
+#define ROUTER_MAX_TOPK 32
+
+template <typename TA, int TOK>
+__global__ void __launch_bounds__(ROUTER_THREADS)
+router_topk_kernel(const TA* __restrict__ x, const float* __restrict__ w,
+                   const float* __restrict__ extra_w, int T, int H, int E, int k, int renorm,
+                   float scale, float* __restrict__ topk_w, int* __restrict__ topk_idx,
+                   float* __restrict__ extra_out) {
+  extern __shared__ float smem[];
+  float* xs = smem;                         // [TOK][H]
+  float* lg = smem + (size_t)TOK * H;       // [TOK][E]
+  const int t0 = blockIdx.x * TOK;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = ROUTER_THREADS / 32;
+  for (int idx = threadIdx.x; idx < TOK * H; idx += ROUTER_THREADS) {
+    const int tk = idx / H, i = idx - tk * H;
+    const int t = t0 + tk;
+    xs[idx] = t < T ? to_f32(x[(size_t)t * H + i]) : 0.f;
+  }
+  __syncthreads();
+  const int rows_total = E + (extra_w ? 1 : 0);
+  for (int e = warp; e < rows_total; e += nwarps) {
+    const float* wr = e < E ? w + (size_t)e * H : extra_w;
+    float acc[TOK];
+#pragma unroll
+    for (int tk = 0; tk < TOK; ++tk) acc[tk] = 0.f;
+    for (int i = lane; i < H; i += 32) {
+      const float wv = wr[i];
+#pragma unroll
+      for (int tk = 0; tk < TOK; ++tk) acc[tk] += xs[tk * H + i] * wv;
+    }
+#pragma unroll
+    for (int tk = 0; tk < TOK; ++tk) {
+      const float v = warp_sum(acc[tk]);
+      if (lane == 0) {
+        if (e < E) lg[tk * E + e] = v;
+        else if (t0 + tk < T) extra_out[t0 + tk] = v;
+      }
+    }
+  }
+  __syncthreads();
+  // softmax + top-k: one warp per token
+  for (int tk = warp; tk < TOK; tk += nwarps) {
+    const int t = t0 + tk;
+    if (t >= T) continue;
+    float* p = lg + tk * E;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, p[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float v = expf(p[e] - mx);
+      p[e] = v;
+      sum += v;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    float total = 0.f;
+    float my_w = 0.f;  // lane s keeps slot s
+    int my_i = 0;
+    for (int s = 0; s < k; ++s) {
+      float best = -1.f;
+      int bi = 0x7fffffff;
+      for (int e = lane; e < E; e += 32) {
+        const float v = p[e];
+        if (v > best) { best = v; bi = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      const float prob = best / sum;
+      if (lane == s) { my_w = prob; my_i = bi; }
+      total += prob;
+      if (lane == 0) p[bi] = -2.f;  // masked: below every probability
+      __syncwarp();
+    }
+    if (lane < k) {
+      float wv = my_w;
+      if (renorm && total > 0.f) wv = wv / total;
+      wv *= scale;
+      topk_w[(size_t)t * k + lane] = wv;
+      topk_idx[(size_t)t * k + lane] = my_i;
+    }
+  }
+}
+
+template <typename TA, int TOK>
+static int launch_router(const void* x, const float* w, const float* extra_w, int T, int H, int E,
+                         int k, int renorm, float scale, float* topk_w, int* topk_idx,
+                         float* extra_out, cudaStream_t stream) {
+  const size_t smem = ((size_t)TOK * H + (size_t)TOK * E) * sizeof(float);
+  if (smem > 200 * 1024) return IX_ERR_SMEM;
+  auto kern = router_topk_kernel<TA, TOK>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int blocks = (T + TOK - 1) / TOK;
+  kern<<<blocks, ROUTER_THREADS, smem, stream>>>((const TA*)x, w, extra_w, T, H, E, k, renorm,
+                                                 scale, topk_w, topk_idx, extra_out);
+  return ix_launch_status();
+}
+
+IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, int act_dtype,
+                          int T, int H, int E, int k, int renorm, float scale, float* topk_w,
+                          int* topk_idx, float* extra_out, cudaStream_t stream) {
+  if (T <= 0) return IX_OK;
+  if (H <= 0 || E <= 0 || k <= 0 || k > E || k > ROUTER_MAX_TOPK) return IX_ERR_SIZE;
+  if (extra_w && !extra_out) return IX_ERR_SIZE;
+  // many tokens share one pass over the router weights; few tokens spread out
+  const size_t per_tok = ((size_t)H + E) * sizeof(float);
+  int tok = T >= 8 * 148 ? 8 : (T >= 2 * 148 ? 2 : 1);
+  while (tok > 1 && tok * per_tok > 96 * 1024) tok >>= 1;
+  IX_DISPATCH_DTYPE(act_dtype, TA, {
+    if (tok == 8)
+      return launch_router<TA, 8>(x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx,
+                                  extra_out, stream);
+    if (tok == 4)
+      return launch_router<TA, 4>(x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx,
+                                  extra_out, stream);
+    if (tok == 2)
+      return launch_router<TA, 2>(x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx,
+                                  extra_out, stream);
+    return launch_router<TA, 1>(x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx,
+                                extra_out, stream);
+  });
+  return IX_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Dispatch tables.  One block; each warp owns experts warp, warp+32, ... and
+// walks the assignment list with ballots, so the order inside an expert is the
+// assignment order and no atomics are involved.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+moe_dispatch_kernel(const int* __restrict__ topk_idx, int A, int E, int k,
+                    int* __restrict__ offsets, int* __restrict__ rows, int* __restrict__ dest) {
+  extern __shared__ int counts[];  // [E + 1]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nwarps) {
+    int c = 0;
+    for (int a0 = 0; a0 < A; a0 += 32) {
+      const int a = a0 + lane;
+      const bool hit = a < A && topk_idx[a] == e;
+      c += __popc(__ballot_sync(0xffffffffu, hit));
+    }
+    if (lane == 0) counts[e] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = counts[e];
+      counts[e] = run;
+      offsets[e] = run;
+      run += c;
+    }
+    counts[E] = run;
+    offsets[E] = run;
+  }
+  __syncthreads();
+  for (int e = warp; e < E; e += nwarps) {
+    int base = counts[e];
+    for (int a0 = 0; a0 < A; a0 += 32) {
+      const int a = a0 + lane;
+      const bool hit = a < A && topk_idx[a] == e;
+      const unsigned mask = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const int r = base + __popc(mask & ((1u << lane) - 1u));
+        rows[r] = a / k;
+        dest[a] = r;
+      }
+      base += __popc(mask);
+    }
+  }
+}
+
+IX_API int ix_moe_dispatch(const int* topk_idx, int T, int E, int k, int* offsets, int* rows,
+                           int* dest, cudaStream_t stream) {
+  if (E <= 0 || k <= 0 || E > 8192) return IX_ERR_SIZE;
+  if (T < 0) return IX_ERR_SIZE;
+  const int A = T * k;
+  const int threads = E >= 32 ? 1024 : 32 * E;
+  moe_dispatch_kernel<<<1, threads, (E + 1) * sizeof(int), stream>>>(topk_idx, A, E, k, offsets,
+                                                                    rows, dest);
+  return ix_launch_status();
+}

@@ -1,0 +1,181 @@
+// Next-token choice from fp32 logits, one block per row.
+//
+// Reference behaviour: ArgmaxKernel (src/backends/cuda/ops/layers.cu:413-452,
+// ties go to the lower index) and SampleKernel (layers.cu:1051-1303): greedy when
+// temperature <= 0; otherwise p_i ~ exp(logit_i / t - max), a probability cutoff
+// found by bisection for top-k (the k-th largest) and for top-p (the smallest
+// head of the distribution whose mass reaches top_p), the min-p floor
+// min_p * p_max in closed form, one uniform from a counter-based generator keyed
+// by the row's seed, and an inverse-CDF walk in index order over the kept
+// tokens.  The host twin is src/engine/host_sampling.cc:50-111.
+//
+// The uniform comes from splitmix64(seed) (top 24 bits), so the host can compute
+// the same number without a device.
+#include "common.cuh"
+
+#define SAMPLE_THREADS 1024
+
+__device__ __forceinline__ float uniform_from_seed(unsigned long long seed) {
+  unsigned long long z = seed + 0x9e3779b97f4a7c15ULL;
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ULL;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebULL;
+  z ^= z >> 31;
+  return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float m = -INFINITY;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, scratch[w]);
+  return m;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
+              const float* __restrict__ top_p, const int* __restrict__ top_k,
+              const float* __restrict__ min_p, const unsigned long long* __restrict__ seeds,
+              int* __restrict__ out) {
+  __shared__ float scratch[32];
+  __shared__ int scratch_i[32];
+  __shared__ float csum[SAMPLE_THREADS];
+  __shared__ int s_chunk;
+  __shared__ float s_base;
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * V;
+  const float t = temperature ? temperature[r] : 0.f;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  if (!(t > 0.f)) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) {
+      const float v = row[i];
+      if (v > best || bi == 0x7fffffff) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) {
+        best = ob; bi = oi;
+      }
+    }
+    if (lane == 0) { scratch[warp] = best; scratch_i[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float b = scratch[0];
+      int idx = scratch_i[0];
+      for (int w = 1; w < SAMPLE_THREADS / 32; ++w) {
+        const float ob = scratch[w];
+        const int oi = scratch_i[w];
+        if (oi != 0x7fffffff && (idx == 0x7fffffff || ob > b || (ob == b && oi < idx))) {
+          b = ob; idx = oi;
+        }
+      }
+      out[r] = idx == 0x7fffffff ? 0 : idx;
+    }
+    return;
+  }
+
+  const float inv_t = 1.0f / t;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, row[i] * inv_t);
+  mx = block_max(mx, scratch);
+  float part = 0.f;
+  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) part += expf(row[i] * inv_t - mx);
+  const float total = block_sum(part, scratch);
+
+  // probability cutoff in units where p_max = 1
+  float cut = 0.f;
+  const float mp = min_p ? min_p[r] : 0.f;
+  if (mp > 0.f) cut = fminf(mp, 1.0f);
+  const int tk = top_k ? top_k[r] : 0;
+  if (tk > 0 && tk < V) {
+    float lo = 0.f, hi = 1.f;
+    for (int it = 0; it < 32; ++it) {
+      const float mid = 0.5f * (lo + hi);
+      float cnt = 0.f;
+      for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS)
+        cnt += expf(row[i] * inv_t - mx) >= mid ? 1.f : 0.f;
+      cnt = block_sum(cnt, scratch);
+      if (cnt >= (float)tk) lo = mid; else hi = mid;
+    }
+    cut = fmaxf(cut, lo);
+  }
+  const float tp = top_p ? top_p[r] : 1.f;
+  if (tp < 1.f) {
+    float lo = cut, hi = 1.f;
+    for (int it = 0; it < 32; ++it) {
+      const float mid = 0.5f * (lo + hi);
+      float mass = 0.f;
+      for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) {
+        const float p = expf(row[i] * inv_t - mx);
+        mass += p >= mid ? p : 0.f;
+      }
+      mass = block_sum(mass, scratch);
+      if (mass >= tp * total) lo = mid; else hi = mid;
+    }
+    cut = lo;
+  }
+
+  // inverse CDF in index order over the kept tokens; thread i owns a contiguous chunk
+  const int chunk = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+  const int c0 = threadIdx.x * chunk;
+  const int c1 = min(V, c0 + chunk);
+  float mine = 0.f;
+  for (int i = c0; i < c1; ++i) {
+    const float p = expf(row[i] * inv_t - mx);
+    if (p >= cut) mine += p;
+  }
+  csum[threadIdx.x] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float run = 0.f;
+    for (int i = 0; i < SAMPLE_THREADS; ++i) run += csum[i];
+    const float target = uniform_from_seed(seeds ? seeds[r] : 0ULL) * run;
+    float acc = 0.f;
+    int pick = -1, last = 0;
+    float base = 0.f, last_base = 0.f;
+    for (int i = 0; i < SAMPLE_THREADS; ++i) {
+      const float c = csum[i];
+      if (c > 0.f) {
+        last = i; last_base = acc;
+        if (acc + c >= target) { pick = i; base = acc; break; }
+      }
+      acc += c;
+    }
+    if (pick < 0) { pick = last; base = last_base; }
+    s_chunk = pick;
+    s_base = base;
+    csum[0] = target;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x == s_chunk) {
+    const float target = csum[0];
+    float run = s_base;
+    int chosen = -1, last = c0;
+    for (int i = c0; i < c1; ++i) {
+      const float p = expf(row[i] * inv_t - mx);
+      if (p >= cut) {
+        run += p;
+        last = i;
+        if (run >= target) { chosen = i; break; }
+      }
+    }
+    out[r] = chosen >= 0 ? chosen : last;
+  }
+}
+
+IX_API int ix_sample(const float* logits, int R, int V, const float* temperature,
+                     const float* top_p, const int* top_k, const float* min_p,
+                     const unsigned long long* seeds, int* out, cudaStream_t stream) {
+  if (R <= 0) return IX_OK;
+  if (V <= 0) return IX_ERR_SIZE;
+  sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, top_p, top_k, min_p,
+                                                  seeds, out);
+  return ix_launch_status();
+}

@@ -1,0 +1,369 @@
+"""Python faces of the CUDA kernels: argument checks, output allocation, launch.
+
+Every function takes CUDA tensors and launches on torch's current stream, so a
+step can be captured into a CUDA graph.  A CPU tensor, a non-contiguous tensor,
+a wrong element type or a size the kernel does not take raises; nothing here
+falls back to a library implementation.
+
+Matrix products without a fused epilogue go to cuBLAS through ``torch`` in the
+bfloat16 mode, where the reference engine also calls a library
+(src/backends/cuda/ops/gemm_cublaslt.cc:391-396); the 32-bit mode runs the
+library's own fp32 FFMA kernel so that no reduced-precision matrix mode can
+enter.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import library
+
+F32, BF16 = 0, 1
+
+_ERRORS = {
+    -1: "element type not supported by this kernel",
+    -2: "a size this kernel does not take",
+    -3: "pointer or stride not aligned as the kernel requires",
+    -4: "shared memory need exceeds the device limit for these sizes",
+    -5: "this combination of options is not built",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"element type {t.dtype} is not float32 or bfloat16")
+
+
+def _chk(name: str, t: Optional[torch.Tensor], dtype=None, optional: bool = False):
+    if t is None:
+        if optional:
+            return
+        raise KernelError(f"{name}: tensor required")
+    if not isinstance(t, torch.Tensor):
+        raise KernelError(f"{name}: expected a tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise KernelError(
+            f"{name}: tensor is on {t.device}; the kernels run on a CUDA device only "
+            "(there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: tensor must be contiguous, strides {t.stride()}")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str):
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _lib():
+    return library.load()
+
+
+LAUNCHES = [0]  # number of kernel launches issued through this module
+
+
+def _count(n: int = 1):
+    LAUNCHES[0] += n
+
+
+# ---------------------------------------------------------------------------
+def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None):
+    """out[t] = table[ids[t]] widened to fp32 (the residual stream)."""
+    _chk("table", table)
+    _chk("ids", ids, torch.int32)
+    V, H = table.shape
+    T = ids.numel()
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _chk("out", out, torch.float32)
+    _check(_lib().ix_embed(_ptr(table), _dtype_code(table), _ptr(ids), T, H, V, _ptr(out),
+                           _stream()), "embed")
+    _count()
+    return out
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor,
+                eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
+    """resid += delta (kept when ``rows`` is None); returns RMSNorm(resid) * gain.
+
+    With ``rows`` the listed rows are gathered, normalised and returned without
+    writing the residual back."""
+    _chk("resid", resid, torch.float32)
+    _chk("gain", gain, torch.float32)
+    _chk("delta", delta, optional=True)
+    _chk("rows", rows, torch.int32, optional=True)
+    T, H = resid.shape
+    if gain.numel() != H:
+        raise KernelError(f"add_rmsnorm: gain has {gain.numel()} entries, rows have {H}")
+    if delta is not None and (delta.shape != resid.shape or delta.dtype != out_dtype):
+        raise KernelError("add_rmsnorm: delta must match the residual's shape and the "
+                          f"activation type ({tuple(delta.shape)}, {delta.dtype})")
+    R = T if rows is None else rows.numel()
+    out = torch.empty((R, H), dtype=out_dtype, device=resid.device)
+    _check(_lib().ix_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(gain), _ptr(rows), _ptr(out),
+                                 _dtype_code(out), R, H, ctypes.c_float(eps),
+                                 1 if rows is None else 0, _stream()), "add_rmsnorm")
+    _count()
+    return out
+
+
+def silu_mul(gu: torch.Tensor):
+    _chk("gu", gu)
+    T, two_i = gu.shape
+    if two_i % 2:
+        raise KernelError("silu_mul: width must be even (gate | up)")
+    out = torch.empty((T, two_i // 2), dtype=gu.dtype, device=gu.device)
+    _check(_lib().ix_silu_mul(_ptr(gu), _ptr(out), _dtype_code(gu), T, two_i // 2, _stream()),
+           "silu_mul")
+    _count()
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None):
+    """x[M,K] . w[N,K]^T.  bfloat16: cuBLAS, fp32 accumulation.  float32: own FFMA kernel."""
+    _chk("x", x)
+    _chk("w", w)
+    if x.dtype != w.dtype:
+        raise KernelError(f"linear: activations are {x.dtype} but weights are {w.dtype}")
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"linear: inner sizes differ ({K} vs {K2})")
+    out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.bfloat16:
+        _count()
+        if out_dtype == torch.bfloat16:
+            return torch.mm(x, w.t())
+        return torch.mm(x, w.t(), out_dtype=out_dtype)
+    return gemm_generic(x, w.unsqueeze(0), None, None, dual=False, out_dtype=out_dtype)
+
+
+def gemm_generic(x: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor],
+                 offsets: Optional[torch.Tensor], dual: bool,
+                 out_dtype: Optional[torch.dtype] = None, num_out_rows: Optional[int] = None):
+    """CUDA-core product, single (offsets None) or grouped by expert."""
+    _chk("x", x)
+    _chk("w", w)
+    _chk("rows", rows, torch.int32, optional=True)
+    _chk("offsets", offsets, torch.int32, optional=True)
+    E, w_rows, K = w.shape
+    N = w_rows // 2 if dual else w_rows
+    if x.shape[1] != K:
+        raise KernelError(f"gemm: inner sizes differ ({x.shape[1]} vs {K})")
+    out_dtype = out_dtype or x.dtype
+    if offsets is None:
+        M = x.shape[0]
+        A = M
+    else:
+        M = 0
+        A = num_out_rows if num_out_rows is not None else (
+            rows.numel() if rows is not None else x.shape[0])
+    out = torch.empty((A, N), dtype=out_dtype, device=x.device)
+    code = _lib().ix_gemm_generic(
+        _ptr(x), _ptr(rows), _ptr(offsets), _ptr(w), _ptr(out), _dtype_code(x),
+        F32 if out_dtype == torch.float32 else BF16, 1 if dual else 0, M, N, K, E, A, _stream())
+    _check(code, "gemm_generic")
+    _count()
+    return out
+
+
+def qkv_rope_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
+                    inv_freq: Optional[torch.Tensor], rotary_dim: int, heads: int, kv_heads: int,
+                    head_dim: int, k_cache: Optional[torch.Tensor],
+                    v_cache: Optional[torch.Tensor], slots: Optional[torch.Tensor],
+                    want_dense_kv: bool = False):
+    """Split + bias + rotate; returns q [T,heads,hd] (and dense k, v when asked);
+    writes k, v into the paged cache at ``slots`` when a cache is given."""
+    _chk("qkv", qkv)
+    _chk("bias", bias, torch.float32, optional=True)
+    _chk("positions", positions, torch.int32)
+    _chk("inv_freq", inv_freq, torch.float32, optional=True)
+    _chk("slots", slots, torch.int32, optional=True)
+    T, width = qkv.shape
+    if width != (heads + 2 * kv_heads) * head_dim:
+        raise KernelError(f"qkv_rope_append: row width {width} is not (heads+2*kv_heads)*head_dim")
+    if bias is not None and bias.numel() != width:
+        raise KernelError("qkv_rope_append: bias length does not match the fused row")
+    if rotary_dim and (inv_freq is None or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("qkv_rope_append: inv_freq must have rotary_dim/2 entries")
+    page_size = 1
+    if k_cache is not None:
+        _chk("k_cache", k_cache, qkv.dtype)
+        _chk("v_cache", v_cache, qkv.dtype)
+        if slots is None:
+            raise KernelError("qkv_rope_append: a cache needs slots")
+        P, ckv, page_size, chd = k_cache.shape
+        if ckv != kv_heads or chd != head_dim or v_cache.shape != k_cache.shape:
+            raise KernelError("qkv_rope_append: cache geometry does not match the heads")
+    q = torch.empty((T, heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    k = v = None
+    if want_dense_kv:
+        k = torch.empty((T, kv_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+        v = torch.empty_like(k)
+    code = _lib().ix_qkv_rope_append(
+        _ptr(qkv), _ptr(bias), _ptr(positions), _ptr(inv_freq), rotary_dim, _ptr(slots), _ptr(q),
+        _ptr(k_cache), _ptr(v_cache), page_size, _ptr(k), _ptr(v), _dtype_code(qkv), T, heads,
+        kv_heads, head_dim, _stream())
+    _check(code, "qkv_rope_append")
+    _count()
+    return (q, k, v) if want_dense_kv else q
+
+
+def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                            block_table: torch.Tensor, seq_of_token: torch.Tensor,
+                            positions: torch.Tensor, window: int, scale: float):
+    _chk("q", q)
+    _chk("k_cache", k_cache, q.dtype)
+    _chk("v_cache", v_cache, q.dtype)
+    _chk("block_table", block_table, torch.int32)
+    _chk("seq_of_token", seq_of_token, torch.int32)
+    _chk("positions", positions, torch.int32)
+    T, heads, hd = q.shape
+    P, kvh, page, chd = k_cache.shape
+    if chd != hd:
+        raise KernelError("paged_attention: cache head size differs from the query's")
+    out = torch.empty_like(q)
+    code = _lib().ix_paged_attention_generic(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(seq_of_token),
+        _ptr(positions), _ptr(out), _dtype_code(q), T, heads, kvh, hd, page,
+        block_table.shape[1], window, ctypes.c_float(scale), _stream())
+    _check(code, "paged_attention_generic")
+    _count()
+    return out
+
+
+def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, renormalize: bool, scale: float,
+                extra_w: Optional[torch.Tensor] = None
+                ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """fp32 router logits, softmax over all experts, top-k (ties to the lower index).
+
+    Returns (weights [T,k] fp32, experts [T,k] int32, x.extra_w [T] fp32 or None)."""
+    _chk("x", x)
+    _chk("w", w, torch.float32)
+    _chk("extra_w", extra_w, torch.float32, optional=True)
+    T, H = x.shape
+    E = w.shape[0]
+    if w.shape[1] != H or (extra_w is not None and extra_w.numel() != H):
+        raise KernelError("router_topk: weight width differs from the activations'")
+    tw = torch.empty((T, top_k), dtype=torch.float32, device=x.device)
+    ti = torch.empty((T, top_k), dtype=torch.int32, device=x.device)
+    ex = torch.empty((T,), dtype=torch.float32, device=x.device) if extra_w is not None else None
+    code = _lib().ix_router_topk(_ptr(x), _ptr(w), _ptr(extra_w), _dtype_code(x), T, H, E, top_k,
+                                 1 if renormalize else 0, ctypes.c_float(scale), _ptr(tw),
+                                 _ptr(ti), _ptr(ex), _stream())
+    _check(code, "router_topk")
+    _count()
+    return tw, ti, ex
+
+
+def moe_dispatch(topk_idx: torch.Tensor, num_experts: int):
+    """offsets[E+1], rows[A] (token of each grouped row), dest[A] (grouped row of t*k+slot)."""
+    _chk("topk_idx", topk_idx, torch.int32)
+    T, k = topk_idx.shape
+    dev = topk_idx.device
+    offsets = torch.empty((num_experts + 1,), dtype=torch.int32, device=dev)
+    rows = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    dest = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    _check(_lib().ix_moe_dispatch(_ptr(topk_idx), T, num_experts, k, _ptr(offsets), _ptr(rows),
+                                  _ptr(dest), _stream()), "moe_dispatch")
+    _count()
+    return offsets, rows, dest
+
+
+def moe_combine(y: torch.Tensor, dest: torch.Tensor, topk_w: torch.Tensor,
+                shared: Optional[torch.Tensor], shared_logit: Optional[torch.Tensor]):
+    _chk("y", y)
+    _chk("dest", dest, torch.int32)
+    _chk("topk_w", topk_w, torch.float32)
+    _chk("shared", shared, y.dtype, optional=True)
+    _chk("shared_logit", shared_logit, torch.float32, optional=True)
+    T, k = topk_w.shape
+    H = y.shape[1]
+    out = torch.empty((T, H), dtype=y.dtype, device=y.device)
+    _check(_lib().ix_moe_combine(_ptr(y), _ptr(dest), _ptr(topk_w), _ptr(shared),
+                                 _ptr(shared_logit), _ptr(out), _dtype_code(y), T, H, k,
+                                 _stream()), "moe_combine")
+    _count()
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           seeds: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
+           top_k: Optional[torch.Tensor] = None, min_p: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None):
+    """Token ids [R] int32 from fp32 logits [R,V]; greedy where temperature <= 0 or absent."""
+    _chk("logits", logits, torch.float32)
+    _chk("temperature", temperature, torch.float32, optional=True)
+    _chk("seeds", seeds, torch.int64, optional=True)
+    _chk("top_p", top_p, torch.float32, optional=True)
+    _chk("top_k", top_k, torch.int32, optional=True)
+    _chk("min_p", min_p, torch.float32, optional=True)
+    R, V = logits.shape
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _chk("out", out, torch.int32)
+    _check(_lib().ix_sample(_ptr(logits), R, V, _ptr(temperature), _ptr(top_p), _ptr(top_k),
+                            _ptr(min_p), _ptr(seeds), _ptr(out), _stream()), "sample")
+    _count()
+    return out
+
+
+def append_kv(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              slots: torch.Tensor):
+    """Write dense k, v rows [T,kv_heads,hd] into the paged cache at ``slots``."""
+    _chk("k", k)
+    _chk("v", v, k.dtype)
+    _chk("k_cache", k_cache, k.dtype)
+    _chk("v_cache", v_cache, k.dtype)
+    _chk("slots", slots, torch.int32)
+    T, kvh, hd = k.shape
+    P, ckv, page, chd = k_cache.shape
+    if (ckv, chd) != (kvh, hd) or v.shape != k.shape or v_cache.shape != k_cache.shape:
+        raise KernelError("append_kv: cache geometry does not match the rows")
+    _check(_lib().ix_append_kv(_ptr(k), _ptr(v), _ptr(slots), _ptr(k_cache), _ptr(v_cache), page,
+                               _dtype_code(k), T, kvh, hd, _stream()), "append_kv")
+    _count()
+
+
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    block_table: torch.Tensor, step, window: int, scale: float):
+    """Causal attention of this step's queries over the paged cache.
+
+    ``step`` carries the batch description (``seq_of_token``, ``positions``, ``cu_q``,
+    ``q_pos0``, ``kv_len``, ``max_q_len``, ``max_kv_len``, ``all_decode``)."""
+    return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,
+                                   step.positions, window, scale)
+
+
+def grouped_gate_up_swiglu(x: torch.Tensor, rows: torch.Tensor, offsets: torch.Tensor,
+                           w_gate_up: torch.Tensor):
+    """act[r] = silu(x[rows[r]] . Wg[e]^T) * (x[rows[r]] . Wu[e]^T), e from offsets.
+
+    ``w_gate_up``: [E, 2I, H], per expert the gate rows then the up rows."""
+    return gemm_generic(x, w_gate_up, rows, offsets, dual=True, num_out_rows=rows.numel())
+
+
+def grouped_down(act: torch.Tensor, offsets: torch.Tensor, w_down: torch.Tensor):
+    """y[r] = act[r] . Wd[e]^T with ``w_down`` [E, H, I]."""
+    return gemm_generic(act, w_down, None, offsets, dual=False, num_out_rows=act.shape[0])

@@ -1,0 +1,92 @@
+"""What every part sees: the build context, the per-step context, cache needs.
+
+Interfaces (duck-typed; a part defined outside this package works the same):
+
+* every part: ``__init__(spec, ctx: BuildContext, prefix: str)``,
+  ``tensors() -> [TensorDecl]`` (full checkpoint names), ``bind(weights: dict)``
+  (receives exactly the declared tensors, on the device, already converted).
+* norm: ``forward(resid, delta, rows=None) -> normed``; adds ``delta`` into the
+  fp32 residual in place (unless ``rows`` picks rows to gather) and returns the
+  normalised activations in the run's element type.
+* position encoding: ``rotary_table() -> (inv_freq fp32 [rotary_dim/2] | None,
+  rotary_dim)``; optionally ``apply(q, k, positions)`` for encodings that are not
+  a rotation table (called on dense q and k before k enters the cache).
+* mixer: ``cache_needs() -> [PagedKvNeed | StateNeed]``,
+  ``forward(x, step: StepContext, cache: LayerCache) -> [T, hidden]``.
+* feed-forward: ``forward(x, step) -> [T, hidden]``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+
+
+@dataclass
+class BuildContext:
+    dtype: torch.dtype          # element type of activations and matrices
+    device: torch.device
+    ops: Any                    # the kernel module (inferx_b200.kernels.ops)
+
+
+@dataclass(frozen=True)
+class PagedKvNeed:
+    """Keys and values per token, in pages.  ``window`` = 0 keeps every token;
+    otherwise pages wholly behind the last ``window`` tokens may be given back."""
+    kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """State of fixed size per request (not per token), zeroed when a request
+    gets its slot: ``[slots, *shape]`` of ``dtype``."""
+    name: str
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class GroupView:
+    """One cache group's view of the step: where each sequence's pages are and
+    where this step's tokens go."""
+    block_table: torch.Tensor   # [S, max_blocks] int32, -1 where no page is held
+    slots: torch.Tensor         # [T] int32: page * page_size + offset
+    page_size: int
+    window: int
+
+
+@dataclass
+class StepContext:
+    """One batch: tokens of several sequences, grouped by sequence in ascending
+    sequence index with contiguous positions inside a sequence."""
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor     # [T] int32
+    positions: torch.Tensor     # [T] int32
+    seq_of_token: torch.Tensor  # [T] int32
+    cu_q: torch.Tensor          # [S+1] int32: token range of each sequence
+    q_pos0: torch.Tensor        # [S] int32: position of each sequence's first token here
+    kv_len: torch.Tensor        # [S] int32: tokens each sequence holds after this step
+    state_slot: torch.Tensor    # [S] int32
+    groups: List[GroupView]
+    max_q_len: int
+    max_kv_len: int
+    # host mirrors, for parts that need loop bounds or launch shapes
+    q_lens: List[int] = field(default_factory=list)
+    kv_lens: List[int] = field(default_factory=list)
+    all_decode: bool = False
+
+
+@dataclass
+class LayerCache:
+    """What one run of a layer gets from the cache: the key and value pages of
+    the layer it reads (its own unless the schedule says otherwise), the group
+    whose block table addresses them, and per-request state tensors by name."""
+    group: int = -1
+    k: Optional[torch.Tensor] = None   # [pages, kv_heads, page_size, head_dim]
+    v: Optional[torch.Tensor] = None
+    writes: bool = True
+    state: Dict[str, torch.Tensor] = field(default_factory=dict)

@@ -1,0 +1,107 @@
+"""Feed-forward parts: the dense SwiGLU and the routed mixture of experts.
+
+Dense (src/model/qwen2.cc:1042-1048, 1413-1434): gate and up fused along the
+output dimension, ``silu(gate) * up``, down projection, no biases.
+
+Mixture of experts (src/model/moe_ffn.cc:158-367): router logits -> softmax over
+all experts -> top-k (ties to the lower index) -> optional renormalisation ->
+routed scale; stable dispatch by expert; per expert ``down(silu(gate(x)) *
+up(x))``; combine in slot order with fp32 weights; a shared expert over every
+token whose output is scaled by ``sigmoid(x . w_gate)`` when gated
+(moe_ffn.cc:308-355).  Expert weights are stacked per layer as
+``[E, 2I, H]`` (gate rows then up rows per expert) and ``[E, H, I]``
+(src/model/deepseek_v2.cc:519-556).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..weights.loader import TensorDecl
+from .registry import register_part
+
+
+class SwiGluFeedForward:
+    def __init__(self, spec, ctx, prefix: str):
+        self.spec, self.ctx, self.prefix = spec, ctx, prefix
+        self.gate_up_w = self.down_w = None
+
+    def tensors(self):
+        s, p = self.spec, self.prefix
+        return [
+            TensorDecl(f"{p}.gate_proj.weight", (s.intermediate, s.hidden)),
+            TensorDecl(f"{p}.up_proj.weight", (s.intermediate, s.hidden)),
+            TensorDecl(f"{p}.down_proj.weight", (s.hidden, s.intermediate)),
+        ]
+
+    def bind(self, w):
+        p = self.prefix
+        self.gate_up_w = torch.cat([w[f"{p}.gate_proj.weight"], w[f"{p}.up_proj.weight"]],
+                                   dim=0).contiguous()
+        self.down_w = w[f"{p}.down_proj.weight"]
+
+    def forward(self, x, step=None):
+        ops = self.ctx.ops
+        act = ops.silu_mul(ops.linear(x, self.gate_up_w))
+        return ops.linear(act, self.down_w)
+
+
+class MoeFeedForward:
+    def __init__(self, spec, ctx, prefix: str):
+        self.spec, self.ctx, self.prefix = spec, ctx, prefix
+        if spec.top_k > spec.num_experts:
+            raise ValueError("top_k exceeds the number of experts")
+        self.router_w = self.expert_gate_up = self.expert_down = None
+        self.shared = None
+        self.shared_gate_w = None
+        if spec.shared_intermediate > 0:
+            from .specs import SwiGluSpec
+            self.shared = SwiGluFeedForward(
+                SwiGluSpec(hidden=spec.hidden, intermediate=spec.shared_intermediate), ctx,
+                f"{prefix}.shared_expert")
+
+    def tensors(self):
+        s, p = self.spec, self.prefix
+        decls = [TensorDecl(f"{p}.gate.weight", (s.num_experts, s.hidden), keep="float32")]
+        for e in range(s.num_experts):
+            decls += [
+                TensorDecl(f"{p}.experts.{e}.gate_proj.weight", (s.expert_intermediate, s.hidden)),
+                TensorDecl(f"{p}.experts.{e}.up_proj.weight", (s.expert_intermediate, s.hidden)),
+                TensorDecl(f"{p}.experts.{e}.down_proj.weight", (s.hidden, s.expert_intermediate)),
+            ]
+        if self.shared is not None:
+            decls += self.shared.tensors()
+            if s.shared_gated:
+                decls.append(TensorDecl(f"{p}.shared_expert_gate.weight", (1, s.hidden),
+                                        keep="float32"))
+        return decls
+
+    def bind(self, w):
+        s, p = self.spec, self.prefix
+        self.router_w = w[f"{p}.gate.weight"]
+        gu = torch.empty((s.num_experts, 2 * s.expert_intermediate, s.hidden),
+                         dtype=self.ctx.dtype, device=self.ctx.device)
+        dn = torch.empty((s.num_experts, s.hidden, s.expert_intermediate),
+                         dtype=self.ctx.dtype, device=self.ctx.device)
+        for e in range(s.num_experts):
+            gu[e, :s.expert_intermediate] = w[f"{p}.experts.{e}.gate_proj.weight"]
+            gu[e, s.expert_intermediate:] = w[f"{p}.experts.{e}.up_proj.weight"]
+            dn[e] = w[f"{p}.experts.{e}.down_proj.weight"]
+        self.expert_gate_up, self.expert_down = gu, dn
+        if self.shared is not None:
+            self.shared.bind(w)
+            if s.shared_gated:
+                self.shared_gate_w = w[f"{p}.shared_expert_gate.weight"].reshape(-1).contiguous()
+
+    def forward(self, x, step=None):
+        s, ops = self.spec, self.ctx.ops
+        topk_w, topk_idx, shared_logit = ops.router_topk(
+            x, self.router_w, s.top_k, s.renormalize, s.routed_scale, extra_w=self.shared_gate_w)
+        offsets, rows, dest = ops.moe_dispatch(topk_idx, s.num_experts)
+        act = ops.grouped_gate_up_swiglu(x, rows, offsets, self.expert_gate_up)
+        y = ops.grouped_down(act, offsets, self.expert_down)
+        shared = self.shared.forward(x) if self.shared is not None else None
+        return ops.moe_combine(y, dest, topk_w, shared, shared_logit)
+
+
+register_part("feed_forward", "swiglu", SwiGluFeedForward)
+register_part("feed_forward", "moe", MoeFeedForward)
