@@ -83,10 +83,10 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
 
   const float inv_t = 1.0f / t;
   float mx = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, row[i] * inv_t);
+  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, __fmul_rn(row[i], inv_t));
   mx = block_max(mx, scratch);
   float part = 0.f;
-  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) part += expf(row[i] * inv_t - mx);
+  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) part += expf(__fmul_rn(row[i], inv_t) - mx);
   const float total = block_sum(part, scratch);
 
   // probability cutoff in units where p_max = 1
@@ -100,7 +100,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
       const float mid = 0.5f * (lo + hi);
       float cnt = 0.f;
       for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS)
-        cnt += expf(row[i] * inv_t - mx) >= mid ? 1.f : 0.f;
+        cnt += expf(__fmul_rn(row[i], inv_t) - mx) >= mid ? 1.f : 0.f;
       cnt = block_sum(cnt, scratch);
       if (cnt >= (float)tk) lo = mid; else hi = mid;
     }
@@ -113,7 +113,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
       const float mid = 0.5f * (lo + hi);
       float mass = 0.f;
       for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) {
-        const float p = expf(row[i] * inv_t - mx);
+        const float p = expf(__fmul_rn(row[i], inv_t) - mx);
         mass += p >= mid ? p : 0.f;
       }
       mass = block_sum(mass, scratch);
@@ -128,7 +128,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   const int c1 = min(V, c0 + chunk);
   float mine = 0.f;
   for (int i = c0; i < c1; ++i) {
-    const float p = expf(row[i] * inv_t - mx);
+    const float p = expf(__fmul_rn(row[i], inv_t) - mx);
     if (p >= cut) mine += p;
   }
   csum[threadIdx.x] = mine;
@@ -159,7 +159,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
     float run = s_base;
     int chosen = -1, last = c0;
     for (int i = c0; i < c1; ++i) {
-      const float p = expf(row[i] * inv_t - mx);
+      const float p = expf(__fmul_rn(row[i], inv_t) - mx);
       if (p >= cut) {
         run += p;
         last = i;

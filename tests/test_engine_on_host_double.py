@@ -1,0 +1,39 @@
+"""The engine's host logic (cache manager, step function, replay) against the plain
+model, on the CPU, with the kernels replaced by their plain statements
+(tests/host_ops.py).  What this covers is bookkeeping: positions, slots, block
+tables, page reuse, window release, batching.  The kernels themselves are compared
+on the GPU (``-m gpu``)."""
+import pytest
+import torch
+
+import host_ops
+import model_cases as mc
+import traces
+from conftest import TINY_A, TINY_B
+from inferx_b200.engine.replay import ReplaySession
+
+CASES = [("A", TINY_A, 0, [5, 9, 17, 40, 3, 70], 4), ("B", TINY_B, 1, [1, 6, 13, 31, 45, 80], 8)]
+
+
+@pytest.mark.parametrize("name,cfg,seed,lengths,page", CASES)
+@pytest.mark.parametrize("kind", list(mc.TRACE_KINDS))
+def test_replay_matches_plain(tmp_path, name, cfg, seed, lengths, page, kind):
+    d = mc.make_model_dir(cfg, tmp_path / "m", seed)
+    reqs = mc.make_requests(cfg, lengths, seed)
+    ref = mc.reference_rows(d, reqs)
+    steps = mc.TRACE_KINDS[kind](reqs)
+    sess = ReplaySession(d, "float32", traces.peak_tokens(steps), page_size=page, max_live=4,
+                         device="cpu", ops=host_ops)
+    rows = mc.run_trace(sess, steps)
+    mc.compare(rows, ref, 2e-5, f"{name}/{kind}")
+    if kind in ("whole", "tail", "portions"):
+        assert len(rows) == sum(lengths)
+
+
+def test_pool_too_small_is_reported(tmp_path):
+    d = mc.make_model_dir(TINY_A, tmp_path / "m", 0)
+    reqs = mc.make_requests(TINY_A, [200], 0)
+    from inferx_b200.engine.replay import ReplayError
+    sess = ReplaySession(d, "float32", 64, page_size=16, device="cpu", ops=host_ops)
+    with pytest.raises(ReplayError, match="no page left"):
+        mc.run_trace(sess, traces.whole(reqs))

@@ -1,0 +1,319 @@
+"""Each CUDA kernel alone against its plain fp32 statement (tests/host_ops.py), at
+sizes other than the engine's tiny configurations: head sizes in steps of 16, odd
+numbers of heads and groups, widths and vocabularies that are no power of two."""
+import math
+
+import pytest
+import torch
+
+import host_ops
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from inferx_b200.kernels import ops
+    return ops
+
+
+def _tol(dtype):
+    return dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)
+
+
+def _rand(shape, dtype, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    ops = _ops()
+    table = _rand((301, 72), dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32)
+    out = ops.embed(table.cuda(), ids.cuda())
+    assert out.dtype == torch.float32
+    torch.testing.assert_close(out.cpu(), host_ops.embed(table, ids), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [72, 1000, 2048])
+def test_add_rmsnorm(dtype, H):
+    ops = _ops()
+    resid = _rand((7, H), torch.float32, seed=1)
+    delta = _rand((7, H), dtype, seed=2)
+    gain = 1 + _rand((H,), torch.float32, 0.1, seed=3)
+    r_dev = resid.clone().cuda()
+    out = ops.add_rmsnorm(r_dev, delta.cuda(), gain.cuda(), 1e-5, dtype)
+    r_ref = resid.clone()
+    ref = host_ops.add_rmsnorm(r_ref, delta, gain, 1e-5, dtype)
+    torch.testing.assert_close(r_dev.cpu(), r_ref, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **_tol(dtype))
+    # gather form: picks rows, adds delta, leaves the residual alone
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    before = r_dev.clone()
+    out2 = ops.add_rmsnorm(r_dev, delta.cuda(), gain.cuda(), 1e-5, dtype, rows=rows.cuda())
+    ref2 = host_ops.add_rmsnorm(r_ref.clone(), delta, gain, 1e-5, dtype, rows=rows)
+    assert torch.equal(before, r_dev)
+    torch.testing.assert_close(out2.cpu().float(), ref2.float(), **_tol(dtype))
+    # no delta
+    out3 = ops.add_rmsnorm(r_dev, None, gain.cuda(), 1e-5, dtype)
+    ref3 = host_ops.add_rmsnorm(r_ref.clone(), None, gain, 1e-5, dtype)
+    torch.testing.assert_close(out3.cpu().float(), ref3.float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    ops = _ops()
+    gu = _rand((9, 2 * 88), dtype, 2.0)
+    torch.testing.assert_close(ops.silu_mul(gu.cuda()).cpu().float(),
+                               host_ops.silu_mul(gu).float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 50, 70), (67, 130, 45), (128, 64, 256)])
+def test_linear(dtype, M, N, K):
+    ops = _ops()
+    x, w = _rand((M, K), dtype, seed=4), _rand((N, K), dtype, 0.2, seed=5)
+    out = ops.linear(x.cuda(), w.cuda())
+    ref = host_ops.linear(x, w)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **_tol(dtype))
+    out32 = ops.linear(x.cuda(), w.cuda(), out_dtype=torch.float32)
+    assert out32.dtype == torch.float32
+    torch.testing.assert_close(out32.cpu(), host_ops.linear(x, w, torch.float32),
+                               rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kvh,hd,rot", [(5, 5, 16, 16), (6, 2, 48, 48), (3, 1, 80, 32),
+                                              (4, 2, 128, 0)])
+def test_qkv_rope_append(dtype, heads, kvh, hd, rot):
+    ops = _ops()
+    T, page, P = 11, 4, 9
+    qkv = _rand((T, (heads + 2 * kvh) * hd), dtype, seed=6)
+    bias = _rand(((heads + 2 * kvh) * hd,), torch.float32, 0.5, seed=7)
+    positions = torch.tensor([0, 1, 2, 3, 100, 101, 7, 8, 9, 31999, 32000], dtype=torch.int32)
+    inv = (10000.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / max(rot, 1))).float()
+    slots = torch.randperm(P * page)[:T].to(torch.int32)
+    kc = torch.zeros(P, kvh, page, hd, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    kc_d, vc_d = kc.clone().cuda(), vc.clone().cuda()
+    q, k, v = ops.qkv_rope_append(qkv.cuda(), bias.cuda(), positions.cuda(),
+                                  inv.cuda() if rot else None, rot, heads, kvh, hd, kc_d, vc_d,
+                                  slots.cuda(), want_dense_kv=True)
+    qr, kr, vr = host_ops.qkv_rope_append(qkv, bias, positions, inv if rot else None, rot, heads,
+                                          kvh, hd, kc, vc, slots, want_dense_kv=True)
+    tol = _tol(dtype)
+    torch.testing.assert_close(q.cpu().float(), qr.float(), **tol)
+    torch.testing.assert_close(k.cpu().float(), kr.float(), **tol)
+    torch.testing.assert_close(v.cpu().float(), vr.float(), **tol)
+    torch.testing.assert_close(kc_d.cpu().float(), kc.float(), **tol)
+    torch.testing.assert_close(vc_d.cpu().float(), vc.float(), **tol)
+    # append_kv writes the same cache
+    kc2, vc2 = torch.zeros_like(kc_d), torch.zeros_like(vc_d)
+    ops.append_kv(k, v, kc2, vc2, slots.cuda())
+    assert torch.equal(kc2, kc_d) and torch.equal(vc2, vc_d)
+
+
+def _paged_case(dtype, heads, kvh, hd, page, window, seq_lens, q_lens, seed=0):
+    """Random paged caches with shuffled pages; queries are the last q_len positions."""
+    g = torch.Generator().manual_seed(seed)
+    S = len(seq_lens)
+    maxb = max(-(-n // page) for n in seq_lens)
+    P = S * maxb + 3
+    perm = torch.randperm(P, generator=g)
+    bt = torch.full((S, maxb), -1, dtype=torch.int32)
+    kc = torch.zeros(P, kvh, page, hd)
+    vc = torch.zeros(P, kvh, page, hd)
+    nxt = 0
+    for s, n in enumerate(seq_lens):
+        for b in range(-(-n // page)):
+            bt[s, b] = perm[nxt]
+            nxt += 1
+        for p in range(n):
+            kc[bt[s, p // page], :, p % page] = torch.randn(kvh, hd, generator=g)
+            vc[bt[s, p // page], :, p % page] = torch.randn(kvh, hd, generator=g)
+    seq_of, pos = [], []
+    for s, (n, ql) in enumerate(zip(seq_lens, q_lens)):
+        seq_of += [s] * ql
+        pos += list(range(n - ql, n))
+    T = len(pos)
+    q = torch.randn(T, heads, hd, generator=g)
+    return (q.to(dtype), kc.to(dtype), vc.to(dtype), bt, torch.tensor(seq_of, dtype=torch.int32),
+            torch.tensor(pos, dtype=torch.int32))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kvh,hd,page,window", [
+    (4, 2, 16, 4, 0), (3, 1, 32, 8, 8), (6, 3, 48, 16, 5), (2, 2, 128, 16, 0), (5, 1, 80, 2, 33)])
+def test_paged_attention_generic(dtype, heads, kvh, hd, page, window):
+    ops = _ops()
+    seq_lens, q_lens = [1, 37, 200, 64], [1, 5, 1, 64]
+    q, kc, vc, bt, seq_of, pos = _paged_case(dtype, heads, kvh, hd, page, window, seq_lens, q_lens)
+    scale = 1.0 / math.sqrt(hd)
+    out = ops.paged_attention_generic(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), seq_of.cuda(),
+                                      pos.cuda(), window, scale)
+    ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, window, scale)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **_tol(dtype))
+
+
+def test_attention_finds_one_far_key():
+    """One key far back among hundreds carries the whole weight: a kernel that skips
+    a page, a tile edge or the first key would miss it."""
+    ops = _ops()
+    heads, kvh, hd, page = 2, 1, 32, 8
+    n = 700
+    for far in (0, 7, 8, 127, 128, 129, 511, 699):
+        q, kc, vc, bt, seq_of, pos = _paged_case(torch.float32, heads, kvh, hd, page, 0, [n], [1],
+                                                 seed=far)
+        kc *= 0.01
+        key = torch.randn(hd) * 3
+        kc[bt[0, far // page], 0, far % page] = key
+        q[0, :, :] = key * 2
+        marker = torch.zeros(hd)
+        marker[0] = 1000.0
+        vc[bt[0, far // page], 0, far % page] = marker
+        out = ops.paged_attention_generic(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), seq_of.cuda(),
+                                          pos.cuda(), 0, 1.0)
+        ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, 0, 1.0)
+        assert ref[0, 0, 0] > 900
+        torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-3)
+
+
+def test_attention_window_edge():
+    """The key just outside the window must not count; the one just inside must."""
+    ops = _ops()
+    heads, kvh, hd, page, W = 1, 1, 16, 4, 9
+    n = 40
+    for which, expect_hit in ((n - W, True), (n - W - 1, False)):
+        q, kc, vc, bt, seq_of, pos = _paged_case(torch.float32, heads, kvh, hd, page, W, [n], [1])
+        kc *= 0.01
+        key = torch.ones(hd)
+        kc[bt[0, which // page], 0, which % page] = key * 4
+        q[0, 0] = key * 4
+        vc[:] = 0
+        vc[bt[0, which // page], 0, which % page, 0] = 1.0
+        out = ops.paged_attention_generic(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), seq_of.cuda(),
+                                          pos.cuda(), W, 1.0)
+        assert (out[0, 0, 0].item() > 0.9) == expect_hit
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,E,k,renorm", [(1, 72, 5, 2, True), (33, 200, 60, 4, False),
+                                            (300, 96, 8, 3, True), (1300, 64, 7, 7, False)])
+def test_router_topk(dtype, T, H, E, k, renorm):
+    ops = _ops()
+    x = _rand((T, H), dtype, seed=8)
+    w = _rand((E, H), torch.float32, 0.3, seed=9)
+    extra = _rand((H,), torch.float32, 0.3, seed=10)
+    tw, ti, ex = ops.router_topk(x.cuda(), w.cuda(), k, renorm, 1.5, extra_w=extra.cuda())
+    rw, ri, rex = host_ops.router_topk(x, w, k, renorm, 1.5, extra_w=extra)
+    assert torch.equal(ti.cpu(), ri)
+    torch.testing.assert_close(tw.cpu(), rw, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(ex.cpu(), rex, rtol=1e-4, atol=1e-4)
+
+
+def test_router_ties_go_to_lower_index():
+    ops = _ops()
+    x = torch.ones(3, 16)
+    w = torch.zeros(6, 16)
+    w[1] = w[4] = 0.5       # experts 1 and 4 tie for first, the rest tie below
+    tw, ti, _ = ops.router_topk(x.cuda(), w.cuda(), 3, False, 1.0)
+    assert ti.cpu().tolist() == [[1, 4, 0]] * 3
+
+
+@pytest.mark.parametrize("T,E,k", [(1, 4, 2), (50, 60, 4), (700, 8, 3), (2048, 60, 4)])
+def test_moe_dispatch(T, E, k):
+    ops = _ops()
+    g = torch.Generator().manual_seed(T)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    off, rows, dest = ops.moe_dispatch(idx.cuda(), E)
+    roff, rrows, rdest = host_ops.moe_dispatch(idx, E)
+    assert torch.equal(off.cpu(), roff)
+    assert torch.equal(rows.cpu(), rrows)
+    assert torch.equal(dest.cpu(), rdest)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,I,E,k", [(1, 64, 32, 4, 2), (70, 96, 48, 8, 3), (300, 72, 40, 5, 2)])
+def test_grouped_experts_and_combine(dtype, T, H, I, E, k):
+    ops = _ops()
+    x = _rand((T, H), dtype, seed=11)
+    wgu = _rand((E, 2 * I, H), dtype, 0.2, seed=12)
+    wd = _rand((E, H, I), dtype, 0.2, seed=13)
+    g = torch.Generator().manual_seed(14)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    tw = torch.rand(T, k, generator=g)
+    off, rows, dest = host_ops.moe_dispatch(idx, E)
+    act = ops.grouped_gate_up_swiglu(x.cuda(), rows.cuda(), off.cuda(), wgu.cuda())
+    ract = host_ops.grouped_gate_up_swiglu(x, rows, off, wgu)
+    torch.testing.assert_close(act.cpu().float(), ract.float(), **_tol(dtype))
+    y = ops.grouped_down(ract.cuda(), off.cuda(), wd.cuda())
+    ry = host_ops.grouped_down(ract, off, wd)
+    torch.testing.assert_close(y.cpu().float(), ry.float(), **_tol(dtype))
+    shared = _rand((T, H), dtype, seed=15)
+    logit = _rand((T,), torch.float32, 2.0, seed=16)
+    out = ops.moe_combine(ry.cuda(), dest.cuda(), tw.cuda(), shared.cuda(), logit.cuda())
+    rout = host_ops.moe_combine(ry, dest, tw, shared, logit)
+    torch.testing.assert_close(out.cpu().float(), rout.float(), **_tol(dtype))
+    out2 = ops.moe_combine(ry.cuda(), dest.cuda(), tw.cuda(), None, None)
+    torch.testing.assert_close(out2.cpu().float(),
+                               host_ops.moe_combine(ry, dest, tw, None, None).float(),
+                               **_tol(dtype))
+
+
+def test_sample_greedy_and_temperature():
+    ops = _ops()
+    g = torch.Generator().manual_seed(3)
+    R, V = 6, 1003
+    logits = torch.randn(R, V, generator=g) * 3
+    logits[2, 10] = logits[2, 900] = 50.0          # tie: lower index wins
+    ids = ops.sample(logits.cuda())
+    assert ids.cpu().tolist() == host_ops.sample(logits).tolist()
+    assert ids[2].item() == 10
+    temp = torch.tensor([0.7, 1.0, 0.0, 1.3, 0.5, 2.0])
+    seeds = torch.tensor([1, 2, 3, 4, 5, 2 ** 62 + 11], dtype=torch.int64)
+    a = ops.sample(logits.cuda(), temp.cuda(), seeds.cuda())
+    b = ops.sample(logits.cuda(), temp.cuda(), seeds.cuda())
+    assert torch.equal(a, b)                       # same seed, same draw
+    ref = host_ops.sample(logits, temp, seeds)
+    assert a.cpu().tolist() == ref.tolist()
+    # top_k = 1 and min_p = 1 are argmax whatever the temperature
+    one = torch.ones(R, dtype=torch.int32)
+    hot = torch.full((R,), 1.5)
+    c = ops.sample(logits.cuda(), hot.cuda(), seeds.cuda(), top_k=one.cuda())
+    d = ops.sample(logits.cuda(), hot.cuda(), seeds.cuda(), min_p=torch.ones(R).cuda())
+    assert c.cpu().tolist() == ids.cpu().tolist() == d.cpu().tolist()
+
+
+def test_sample_distribution_and_filters():
+    ops = _ops()
+    V, N = 50, 4000
+    logits = torch.linspace(0, 4, V).repeat(N, 1)
+    seeds = torch.arange(N, dtype=torch.int64) * 7919 + 13
+    temp = torch.ones(N)
+    ids = ops.sample(logits.cuda(), temp.cuda(), seeds.cuda()).cpu().long()
+    freq = torch.bincount(ids, minlength=V).float() / N
+    p = torch.softmax(logits[0], 0)
+    assert (freq - p).abs().max() < 0.03
+    # top-k 5: only the five most probable tokens ever appear
+    ids = ops.sample(logits.cuda(), temp.cuda(), seeds.cuda(),
+                     top_k=torch.full((N,), 5, dtype=torch.int32).cuda()).cpu()
+    assert ids.min().item() >= V - 5
+    # top-p 0.5: the smallest head whose mass reaches 0.5
+    ids = ops.sample(logits.cuda(), temp.cuda(), seeds.cuda(),
+                     top_p=torch.full((N,), 0.5).cuda()).cpu()
+    c = torch.cumsum(p.flip(0), 0)
+    n_keep = int((c < 0.5).sum().item()) + 1
+    assert ids.min().item() >= V - n_keep
+    assert ids.min().item() <= V - n_keep + 1
+
+
+def test_cpu_tensor_is_refused():
+    ops = _ops()
+    with pytest.raises(ops.KernelError):
+        ops.silu_mul(torch.zeros(2, 4))
+    with pytest.raises(ops.KernelError):
+        ops.linear(torch.zeros(2, 4).cuda(), torch.zeros(3, 4).cuda().to(torch.bfloat16))

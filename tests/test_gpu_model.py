@@ -1,0 +1,71 @@
+"""The engine on the GPU against the plain implementation: each request alone and
+whole; most of it in one step and the last 32 tokens one by one; portions of
+changing size; mixed batches with pages used again; in 32-bit and in bfloat16."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import model_cases as mc
+import traces
+from conftest import ROOT, TINY_A, TINY_B
+from inferx_b200.engine.replay import ReplaySession
+
+pytestmark = pytest.mark.gpu
+
+CASES = [("A", TINY_A, 0, [5, 9, 17, 40, 3, 70], 4), ("B", TINY_B, 1, [1, 6, 13, 31, 45, 80], 8)]
+# error bounds relative to the largest logit of the request: fp32 differs from the
+# plain implementation only by summation order; bfloat16 rounds every activation
+# to 8 bits of mantissa (2^-9 relative) through a few dozen operations
+REL = {"float32": 2e-5, "bfloat16": 4e-2}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,cfg,seed,lengths,page", CASES)
+@pytest.mark.parametrize("kind", list(mc.TRACE_KINDS))
+def test_replay_matches_plain(tmp_path, dtype, name, cfg, seed, lengths, page, kind):
+    store = "float32" if dtype == "float32" else "bfloat16"
+    d = mc.make_model_dir(cfg, tmp_path / "m", seed, dtype=store)
+    reqs = mc.make_requests(cfg, lengths, seed)
+    ref = mc.reference_rows(d, reqs)
+    steps = mc.TRACE_KINDS[kind](reqs)
+    sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=page, max_live=4)
+    rows = mc.run_trace(sess, steps)
+    worst = mc.compare(rows, ref, REL[dtype], f"{name}/{kind}/{dtype}")
+    print(f"{name}/{kind}/{dtype}: worst relative error {worst:.3e}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(tmp_path, dtype):
+    """bin/trace_run as a user runs it: JSON lines in, <step>.f32 files and
+    'done <step>' lines out."""
+    cfg = TINY_B
+    d = mc.make_model_dir(cfg, tmp_path / "m", 5, dtype="bfloat16")
+    reqs = mc.make_requests(cfg, [70, 33, 20, 9, 50], 5)
+    ref = mc.reference_rows(d, reqs)
+    steps = traces.mixed(reqs, max_live=4, seed=1)
+    out = tmp_path / "out"
+    p = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype,
+         "--out", str(out), "--max-tokens", str(traces.peak_tokens(steps))],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+        timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    done = [ln for ln in p.stdout.splitlines() if ln.startswith("done ")]
+    assert done == [f"done {s['step']}" for s in steps]
+    outs = []
+    for s in steps:
+        n = sum(len(e["want"]) for e in s["entries"])
+        path = out / f"{s['step']}.f32"
+        if n == 0:
+            assert not path.exists()
+            outs.append(None)
+        else:
+            outs.append(torch.from_numpy(
+                np.fromfile(path, dtype="<f4").reshape(n, cfg["vocab_size"]).copy()))
+    rows = traces.collect(steps, outs)
+    mc.compare(rows, ref, REL[dtype], f"trace_run/{dtype}")
