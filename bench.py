@@ -1,0 +1,404 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput at Qwen1.5-MoE-A2.7B sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096]
+                    [--layers L] [--impl reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second of the default run:
+random weights at the A2.7B layer sizes, batch 8, context 4096, bfloat16, timed on
+the device with CUDA events over exactly K decode steps after W warm-up steps.
+``e2e`` is the same through ``Engine.step`` (host token ids in through pinned
+memory, sampled ids back to the host every step).  ``prefill`` is one 2,048-token
+prompt in one step; ``points`` holds decode at batch 1 and 64; ``roofline`` is the
+bytes a decode step has to read (every weight it uses once, and the cache of the
+live requests) over its time, against the measured copy bandwidth.
+
+A decode step's working set (gigabytes of weights and cache) is far larger than the
+126 MB L2, so nothing stays resident between timed iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+A27B = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "num_hidden_layers": 24, "hidden_size": 2048, "num_attention_heads": 16,
+    "num_key_value_heads": 16, "head_dim": 128, "num_experts": 60, "num_experts_per_tok": 4,
+    "moe_intermediate_size": 1408, "shared_expert_intermediate_size": 5632,
+    "intermediate_size": 5632, "decoder_sparse_step": 1, "mlp_only_layers": [],
+    "norm_topk_prob": False, "vocab_size": 151936, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "use_sliding_window": False, "tie_word_embeddings": False,
+    "torch_dtype": "bfloat16",
+}
+FULL_LAYERS = 24
+METRIC = "decode tok/s at batch 8, context 4096 (Qwen1.5-MoE-A2.7B sizes)"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            hbm = float(p.get("hbm_gbs") or 0)
+            tf = float(p.get("bf16_tflops_sustained") or p.get("bf16_tflops") or 0)
+            if hbm > 0 and tf > 0:
+                return hbm, tf, "measured"
+        except (OSError, ValueError):
+            pass
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+def weight_bytes(cfg, esize=2):
+    H, L = cfg["hidden_size"], cfg["num_hidden_layers"]
+    dq = cfg["num_attention_heads"] * cfg["head_dim"]
+    dkv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    attn = (dq + 2 * dkv) * H + H * dq
+    shared = 3 * H * cfg["shared_expert_intermediate_size"]
+    expert = 3 * H * cfg["moe_intermediate_size"]
+    head = cfg["vocab_size"] * H
+    small = 4 * ((dq + 2 * dkv) + 2 * H + cfg["num_experts"] * H + H)   # fp32 biases/gains/router
+    return {"per_layer_fixed": (attn + shared) * esize + small, "per_expert": expert * esize,
+            "head": head * esize, "layers": L}
+
+
+def decode_step_bytes(cfg, batch, context, experts_touched_per_layer):
+    wb = weight_bytes(cfg)
+    kv_per_tok = 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2 * cfg["num_hidden_layers"]
+    fixed = wb["layers"] * wb["per_layer_fixed"] + wb["head"]
+    experts = wb["per_expert"] * experts_touched_per_layer * wb["layers"]
+    kv = batch * context * kv_per_tok
+    embed = batch * cfg["hidden_size"] * 2
+    return fixed + experts + kv + embed
+
+
+def prefill_flops(cfg, T):
+    H, L = cfg["hidden_size"], cfg["num_hidden_layers"]
+    dq = cfg["num_attention_heads"] * cfg["head_dim"]
+    dkv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_tok = 2 * ((dq + 2 * dkv) * H + H * dq + cfg["num_experts"] * H
+                   + 3 * H * cfg["moe_intermediate_size"] * cfg["num_experts_per_tok"]
+                   + 3 * H * cfg["shared_expert_intermediate_size"] + H)
+    attn = 4 * cfg["num_attention_heads"] * cfg["head_dim"] * T * T / 2
+    return L * (per_tok * T + attn) + 2 * cfg["vocab_size"] * H
+
+
+def make_runtime(cfg, batch, context, extra_tokens, use_graphs=True):
+    import torch
+    from inferx_b200.engine import Runtime, load_model
+    from inferx_b200.weights.loader import RandomSource
+    _, model = load_model(dtype="bfloat16", device="cuda", config_json=cfg,
+                          source=RandomSource(0, device="cuda"))
+    page = 16
+    pages = batch * (-(-(context + extra_tokens) // page) + 1)
+    rt = Runtime(model, page_size=page, num_pages=pages, max_slots=max(batch, 1),
+                 use_graphs=use_graphs)
+    return rt
+
+
+def fill_context(rt, batch, context):
+    """Requests that already hold ``context - 1`` tokens: random keys and values stand
+    in for a prompt (the timed region is decode only)."""
+    import torch
+    mgr = rt.manager
+    for rid in list(mgr.live_requests()):
+        mgr.close(rid)
+    for t in list(rt.storage.k.values()) + list(rt.storage.v.values()):
+        t.normal_(0.0, 0.5)
+    for i in range(batch):
+        mgr.open(i)
+        assert mgr.reserve(i, context - 1)
+        mgr.advance(i, context - 1)
+
+
+def time_decode(rt, batch, context, steps, warmup, seed=0, sampler_clock=None):
+    import torch
+    from inferx_b200.engine import StepEntry
+    from inferx_b200.kernels import ops
+    fill_context(rt, batch, context)
+    mgr = rt.manager
+    vocab = rt.vocab_size
+    g = torch.Generator().manual_seed(seed)
+    toks = torch.randint(0, vocab, (warmup + steps, batch), generator=g).tolist()
+
+    def one(i):
+        for r in range(batch):
+            assert mgr.reserve(r, mgr.length(r) + 1)
+        logits = rt.executor.step([StepEntry(r, [toks[i][r]], [0]) for r in range(batch)])
+        ids = ops.sample(logits)
+        for r in range(batch):
+            mgr.advance(r, 1)
+        return ids
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    l0, c0 = ops.LAUNCHES[0], ops.LIBRARY_CALLS[0]
+    r0 = rt.executor.graph_replays
+    if sampler_clock:
+        sampler_clock.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    clocks = sampler_clock.stop() if sampler_clock else None
+    per_step_own = getattr(rt.executor, "graph_kernel_count", None)
+    launches = ops.LAUNCHES[0] - l0
+    replays = rt.executor.graph_replays - r0
+    return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launches,
+            "library_calls": ops.LIBRARY_CALLS[0] - c0, "replays": replays, "clocks": clocks}
+
+
+def count_step_kernels(rt, batch, context):
+    """Own kernels and library products in one eager decode step, and the number of
+    distinct experts each sparse layer touched."""
+    import torch
+    from inferx_b200.engine import StepEntry
+    from inferx_b200.kernels import ops
+    from inferx_b200.parts.feed_forward import MoeFeedForward
+    fill_context(rt, batch, context)
+    mgr = rt.manager
+    seen = []
+    orig = ops.moe_dispatch
+
+    def spy(topk_idx, num_experts):
+        seen.append(int(torch.unique(topk_idx).numel()))
+        return orig(topk_idx, num_experts)
+
+    ops.moe_dispatch = spy
+    graphs, rt.executor.use_graphs = rt.executor.use_graphs, False
+    try:
+        g = torch.Generator().manual_seed(1)
+        toks = torch.randint(0, rt.vocab_size, (batch,), generator=g).tolist()
+        for r in range(batch):
+            assert mgr.reserve(r, mgr.length(r) + 1)
+        l0, c0 = ops.LAUNCHES[0], ops.LIBRARY_CALLS[0]
+        logits = rt.executor.step([StepEntry(r, [toks[r]], [0]) for r in range(batch)])
+        ops.sample(logits)
+        torch.cuda.synchronize()
+        own, lib = ops.LAUNCHES[0] - l0, ops.LIBRARY_CALLS[0] - c0
+    finally:
+        ops.moe_dispatch = orig
+        rt.executor.use_graphs = graphs
+    touched = sum(seen) / max(1, len(seen))
+    return own, lib, touched
+
+
+def time_prefill(rt, tokens, reps, warmup):
+    import torch
+    from inferx_b200.engine import StepEntry
+    mgr = rt.manager
+    g = torch.Generator().manual_seed(7)
+    toks = torch.randint(0, rt.vocab_size, (tokens,), generator=g).tolist()
+    times = []
+    for i in range(warmup + reps):
+        for rid in list(mgr.live_requests()):
+            mgr.close(rid)
+        mgr.open("p")
+        assert mgr.reserve("p", tokens)
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        rt.executor.step([StepEntry("p", toks, [tokens - 1])])
+        e.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(s.elapsed_time(e))
+    mgr.close("p")
+    times.sort()
+    return times[len(times) // 2]
+
+
+def time_e2e(cfg, batch, context, steps, warmup):
+    """Decode through the public entry point: host ids in (pinned staging), sampled
+    ids back to the host, every step."""
+    import torch
+    from inferx_b200 import Engine, EngineConfig, SamplingParams
+    total_new = warmup + steps + 2
+    prompt_len = context - total_new
+    eng = Engine.create(EngineConfig(
+        config_json=cfg, dtype="bfloat16", max_num_seqs=batch, max_model_len=context + 8,
+        max_num_batched_tokens=4096, block_size=16,
+        num_gpu_blocks_override=batch * (-(-(context + 8) // 16) + 1)))
+    g = torch.Generator().manual_seed(11)
+    for r in range(batch):
+        eng.submit(torch.randint(0, cfg["vocab_size"], (prompt_len,), generator=g).tolist(),
+                   SamplingParams(max_tokens=total_new, ignore_eos=True))
+    # prefill until every request decodes
+    guard = 0
+    while any(s.pending() != 1 for s in eng.scheduler.running) or eng.scheduler.waiting \
+            or not eng.scheduler.running:
+        eng.step()
+        guard += 1
+        assert guard < 10000
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n = 0
+    for _ in range(steps):
+        n += len(eng.step())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    h2d = eng.runtime.executor.last_h2d_bytes
+    del eng
+    torch.cuda.empty_cache()
+    return {"value": n / dt, "unit": "tok/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": 4 * batch, "ms_per_step": dt / steps * 1e3}
+
+
+def reference_arm():
+    why = ("divedb/InferX is a C++20/CMake project with no Python package (no setup.py or "
+           "pyproject.toml) and needs abseil, CLI11, folly and FlashInfer sources that are absent "
+           "offline; it also cannot load Qwen2-MoE checkpoints at all")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="only the default decode run")
+    ap.add_argument("--no-graphs", action="store_true")
+    args = ap.parse_args(argv)
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from inferx_b200.kernels import ops
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    hbm_peak, tf_peak, peak_src = peaks()
+    cfg = dict(A27B, num_hidden_layers=args.layers)
+    B, C = args.batch, args.context
+    max_b = B if args.skip_points else max(B, 64)
+    rt = make_runtime(cfg, max_b, C, args.steps + args.warmup + 8, use_graphs=not args.no_graphs)
+
+    own, lib, touched = count_step_kernels(rt, B, C)
+    clock = ClockSampler()
+    dec = time_decode(rt, B, C, args.steps, args.warmup, sampler_clock=clock)
+    step_bytes = decode_step_bytes(cfg, B, C, touched)
+    achieved = step_bytes / (dec["ms_per_step"] / 1e3) / 1e9
+    out = {
+        "metric": METRIC, "value": round(dec["tok_s"], 1), "unit": "tok/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dec["ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02), uniform random token ids, random cache",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen1.5-MoE-A2.7B sizes", "global_batch": B, "seq_len": C,
+            "parallelism": "single GPU", "layers": args.layers, "layers_of_config": FULL_LAYERS,
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "experts": cfg["num_experts"], "top_k": cfg["num_experts_per_tok"],
+            "moe_intermediate": cfg["moe_intermediate_size"],
+            "shared_intermediate": cfg["shared_expert_intermediate_size"],
+            "vocab": cfg["vocab_size"], "page_size": 16,
+            "cuda_graphs": not args.no_graphs,
+            "l2": "inputs larger than L2 (GBs of weights and cache per step)",
+        },
+        "clocks": dec["clocks"],
+        "gpu_launches": own * args.steps,
+        "launches_per_step": {"own_kernels": own, "library_gemms": lib},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak,
+                     "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
+                     "peak_source": peak_src, "bytes_per_step": int(step_bytes),
+                     "experts_touched_per_layer": round(touched, 2)},
+    }
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            d = time_decode(rt, b, C, max(8, args.steps // 2), args.warmup)
+            points[f"decode_b{b}"] = round(d["tok_s"], 1)
+            points[f"decode_b{b}_ms"] = round(d["ms_per_step"], 4)
+        pms = time_prefill(rt, 2048, reps=5, warmup=3)
+        fl = prefill_flops(cfg, 2048)
+        out["prefill"] = {"value": round(2048 / (pms / 1e3), 1), "tokens": 2048,
+                          "ms": round(pms, 3),
+                          "frac": round(fl / (pms / 1e3) / (tf_peak * 1e12), 4),
+                          "flops": int(fl), "peak_tflops": tf_peak, "peak_source": peak_src}
+        out["points"] = points
+    del rt
+    torch.cuda.empty_cache()
+    if not args.skip_points:
+        out["e2e"] = time_e2e(cfg, B, C, args.steps, args.warmup)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -108,6 +108,7 @@ class Qwen2MoeConfig:
     max_window_layers: int
     max_position_embeddings: int
     torch_dtype: str
+    eos_token_ids: tuple = ()
     architecture: str = "Qwen2MoeForCausalLM"
 
     ARCHITECTURE = "Qwen2MoeForCausalLM"
@@ -186,6 +187,7 @@ class Qwen2MoeConfig:
             max_window_layers=r.integer("max_window_layers", layers),
             max_position_embeddings=r.integer("max_position_embeddings", 0),
             torch_dtype=dtype,
+            eos_token_ids=_eos_ids(obj, where),
         )
         cfg.validate(where)
         return cfg
@@ -235,9 +237,22 @@ class Qwen2MoeConfig:
         d = asdict(self)
         arch = d.pop("architecture")
         d["mlp_only_layers"] = list(self.mlp_only_layers)
+        eos = d.pop("eos_token_ids")
+        if eos:
+            d["eos_token_id"] = list(eos) if len(eos) > 1 else eos[0]
         d["architectures"] = [arch]
         d["model_type"] = "qwen2_moe"
         return d
+
+
+def _eos_ids(obj, where) -> tuple:
+    v = obj.get("eos_token_id")
+    if v is None:
+        return ()
+    vals = v if isinstance(v, list) else [v]
+    if any(isinstance(x, bool) or not isinstance(x, int) for x in vals):
+        raise ConfigError(f"{where}: 'eos_token_id' must be an integer or a list of integers")
+    return tuple(vals)
 
 
 def load_config_json(model_dir: str) -> dict:

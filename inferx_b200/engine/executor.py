@@ -10,6 +10,12 @@ reference's ``Qwen2Model::Step`` (src/model/qwen2.cc:2246-2277) with
 ``PrepareBatchInputs`` (qwen2.cc:564-817) and ``ForwardBatch::Validate``
 (src/model/forward_batch.cc:5-93): rows grouped by sequence, contiguous
 positions, every index array checked on the host before anything is launched.
+All index arrays of a step travel in one pinned staging buffer and one copy.
+
+Steps in which every request brings exactly one token can be replayed from a CUDA
+graph captured per (batch size, block-table width), the reference's
+``CaptureDecodeGraph`` / ``FindGraph(tokens, seqs, blocks)``
+(qwen2.cc:1588-1712, 2210-2218); like the reference the choice is by shape only.
 
 The executor reads the cache manager (lengths, block tables, slots) and never
 changes it, except for zeroing the state of slots newly handed out.  Pages must
@@ -19,7 +25,7 @@ advances the request's length after the step.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -43,8 +49,41 @@ def _pad4(n: int) -> int:
     return (n + 3) & ~3
 
 
+def _bucket(n: int) -> int:
+    """Block-table widths a graph is captured for: powers of two from 8."""
+    b = 8
+    while b < n:
+        b *= 2
+    return b
+
+
+@dataclass
+class _Layout:
+    """Host-side description of one batch, ready to be copied to the device."""
+    T: int
+    S: int
+    R: int
+    segs: List[List[int]]
+    offs: List[int]
+    total: int
+    widths: List[int]          # block-table width per group
+    q_lens: List[int]
+    kv_lens: List[int]
+
+
+@dataclass
+class _Graph:
+    graph: "torch.cuda.CUDAGraph"
+    dev: torch.Tensor
+    hosts: List[torch.Tensor]          # two pinned staging buffers, used in turn
+    copied: List[Optional["torch.cuda.Event"]]
+    logits: Optional[torch.Tensor]
+    turn: int = 0
+
+
 class Executor:
-    def __init__(self, model, manager: CacheManager, storage: CacheStorage):
+    def __init__(self, model, manager: CacheManager, storage: CacheStorage,
+                 use_graphs: bool = False):
         self.model = model
         self.manager = manager
         self.storage = storage
@@ -52,12 +91,14 @@ class Executor:
         self.vocab = model.spec.vocab_size
         self.caches = storage.layer_caches(model.spec.schedule)
         self.steps_run = 0
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        self._graphs: Dict[Tuple, _Graph] = {}
+        self.graph_replays = 0
+        self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------------
-    def build_context(self, entries: Sequence[StepEntry]):
-        """Validate the batch and lay its index arrays out for the device.
-
-        Returns (StepContext, logit_rows tensor or None, number of wanted rows)."""
+    def _layout(self, entries: Sequence[StepEntry], bucket_tables: bool) -> _Layout:
+        """Validate the batch and lay its index arrays out as lists."""
         mgr = self.manager
         if not entries:
             raise StepError("a step needs at least one entry")
@@ -70,96 +111,161 @@ class Executor:
         kv_len: List[int] = []
         state_slot: List[int] = []
         logit_rows: List[int] = []
-        slots = [[] for _ in mgr.groups]
+        n_groups = len(mgr.groups)
+        slots: List[List[int]] = [[] for _ in range(n_groups)]
         ps = mgr.page_size
+        vocab = self.vocab
         for s, e in enumerate(entries):
-            if e.request in seen:
-                raise StepError(f"request {e.request!r} appears twice in one step")
-            seen.add(e.request)
-            if not mgr.has(e.request):
-                raise StepError(f"request {e.request!r} has no cache (open it first)")
+            rid = e.request
+            if rid in seen:
+                raise StepError(f"request {rid!r} appears twice in one step")
+            seen.add(rid)
+            if not mgr.has(rid):
+                raise StepError(f"request {rid!r} has no cache (open it first)")
             n = len(e.tokens)
             if n == 0:
-                raise StepError(f"request {e.request!r} brings no tokens")
-            start = mgr.length(e.request)
-            if start + n > mgr.capacity(e.request):
+                raise StepError(f"request {rid!r} brings no tokens")
+            start = mgr.length(rid)
+            if start + n > mgr.capacity(rid):
                 raise StepError(
-                    f"request {e.request!r}: positions {start}..{start + n - 1} exceed the "
-                    f"{mgr.capacity(e.request)} tokens its pages hold (reserve first)")
+                    f"request {rid!r}: positions {start}..{start + n - 1} exceed the "
+                    f"{mgr.capacity(rid)} tokens its pages hold (reserve first)")
+            base = len(token_ids)
             for tok in e.tokens:
-                if not (0 <= int(tok) < self.vocab):
-                    raise StepError(f"request {e.request!r}: token id {tok} is outside the "
-                                    f"vocabulary of {self.vocab}")
+                tok = int(tok)
+                if not (0 <= tok < vocab):
+                    raise StepError(f"request {rid!r}: token id {tok} is outside the "
+                                    f"vocabulary of {vocab}")
+                token_ids.append(tok)
             for w in e.want:
-                if not (0 <= int(w) < n):
-                    raise StepError(f"request {e.request!r}: wanted place {w} is not among "
+                w = int(w)
+                if not (0 <= w < n):
+                    raise StepError(f"request {rid!r}: wanted place {w} is not among "
                                     f"its {n} tokens")
-                logit_rows.append(len(token_ids) + int(w))
-            for g in range(len(mgr.groups)):
-                table = mgr.table(e.request, g)
+                logit_rows.append(base + w)
+            for g in range(n_groups):
+                table = mgr.table(rid, g)
+                sl = slots[g]
                 for p in range(start, start + n):
                     page = table[p // ps]
                     if page < 0:
-                        raise StepError(f"request {e.request!r}: page of position {p} was "
+                        raise StepError(f"request {rid!r}: the page of position {p} was "
                                         "given back")
-                    slots[g].append(page * ps + p % ps)
-            token_ids += [int(t) for t in e.tokens]
-            positions += list(range(start, start + n))
-            seq_of_token += [s] * n
+                    sl.append(page * ps + p % ps)
+            positions.extend(range(start, start + n))
+            seq_of_token.extend([s] * n)
             cu_q.append(cu_q[-1] + n)
             q_pos0.append(start)
             kv_len.append(start + n)
-            state_slot.append(mgr.slot(e.request))
-        T, S, R = len(token_ids), len(entries), len(logit_rows)
-        max_blocks = []
-        tables = []
-        for g in range(len(mgr.groups)):
+            state_slot.append(mgr.slot(rid))
+        widths, tables = [], []
+        for g in range(n_groups):
             rows = [mgr.table(e.request, g) for e in entries]
             mb = max(1, max(len(r) for r in rows))
+            if bucket_tables:
+                mb = _bucket(mb)
             flat: List[int] = []
             for r in rows:
-                flat += r + [-1] * (mb - len(r))
-            max_blocks.append(mb)
+                flat.extend(r)
+                flat.extend([-1] * (mb - len(r)))
+            widths.append(mb)
             tables.append(flat)
-
-        # one pinned staging buffer, one copy
         segs = [token_ids, positions, seq_of_token, cu_q, q_pos0, kv_len, state_slot, logit_rows]
-        for g in range(len(mgr.groups)):
+        for g in range(n_groups):
             segs += [slots[g], tables[g]]
         offs, total = [], 0
         for sgm in segs:
             offs.append(total)
             total += _pad4(len(sgm))
-        host = torch.zeros(max(total, 4), dtype=torch.int32)
-        for o, sgm in zip(offs, segs):
+        S = len(entries)
+        return _Layout(T=len(token_ids), S=S, R=len(logit_rows), segs=segs, offs=offs,
+                       total=max(total, 4), widths=widths,
+                       q_lens=[cu_q[i + 1] - cu_q[i] for i in range(S)], kv_lens=kv_len)
+
+    @staticmethod
+    def _fill(host: torch.Tensor, lay: _Layout) -> None:
+        for o, sgm in zip(lay.offs, lay.segs):
             if sgm:
                 host[o:o + len(sgm)] = torch.tensor(sgm, dtype=torch.int32)
-        if self.device.type == "cuda":
-            host = host.pin_memory()
-        dev = host.to(self.device, non_blocking=True)
+
+    def _context(self, dev: torch.Tensor, lay: _Layout, static: bool):
+        mgr = self.manager
 
         def seg(i):
-            return dev[offs[i]:offs[i] + len(segs[i])]
+            return dev[lay.offs[i]:lay.offs[i] + len(lay.segs[i])]
 
         groups = []
         for g, grp in enumerate(mgr.groups):
-            groups.append(GroupView(block_table=seg(9 + 2 * g).view(S, max_blocks[g]),
-                                    slots=seg(8 + 2 * g), page_size=ps, window=grp.window))
-        q_lens = [cu_q[i + 1] - cu_q[i] for i in range(S)]
+            groups.append(GroupView(block_table=seg(9 + 2 * g).view(lay.S, lay.widths[g]),
+                                    slots=seg(8 + 2 * g), page_size=mgr.page_size,
+                                    window=grp.window))
+        max_kv = max(lay.kv_lens)
+        if static:   # a captured graph must hold for every length its table width allows
+            max_kv = max(w for w in lay.widths) * mgr.page_size if lay.widths else max_kv
         ctx = StepContext(
-            num_tokens=T, num_seqs=S, token_ids=seg(0), positions=seg(1), seq_of_token=seg(2),
-            cu_q=seg(3), q_pos0=seg(4), kv_len=seg(5), state_slot=seg(6), groups=groups,
-            max_q_len=max(q_lens), max_kv_len=max(kv_len), q_lens=q_lens, kv_lens=list(kv_len),
-            all_decode=all(n == 1 for n in q_lens))
-        return ctx, (seg(7) if R else None), R
+            num_tokens=lay.T, num_seqs=lay.S, token_ids=seg(0), positions=seg(1),
+            seq_of_token=seg(2), cu_q=seg(3), q_pos0=seg(4), kv_len=seg(5), state_slot=seg(6),
+            groups=groups, max_q_len=max(lay.q_lens), max_kv_len=max_kv,
+            q_lens=list(lay.q_lens), kv_lens=list(lay.kv_lens),
+            all_decode=all(n == 1 for n in lay.q_lens))
+        return ctx, (seg(7) if lay.R else None)
+
+    def build_context(self, entries: Sequence[StepEntry]):
+        """(StepContext, logit_rows tensor or None, number of wanted rows) for an eager step."""
+        lay = self._layout(entries, bucket_tables=False)
+        host = torch.zeros(lay.total, dtype=torch.int32)
+        self._fill(host, lay)
+        if self.device.type == "cuda":
+            host = host.pin_memory()
+        dev = host.to(self.device, non_blocking=True)
+        self.last_h2d_bytes = lay.total * 4
+        ctx, rows = self._context(dev, lay, static=False)
+        return ctx, rows, lay.R
+
+    # ------------------------------------------------------------------
+    def _graph_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        lay = self._layout(entries, bucket_tables=True)
+        wanted = tuple(lay.segs[7])
+        key = (lay.S, tuple(lay.widths), wanted)
+        slot = self._graphs.get(key)
+        if slot is None:
+            host = torch.zeros(lay.total, dtype=torch.int32).pin_memory()
+            dev = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
+            self._fill(host, lay)
+            dev.copy_(host, non_blocking=True)
+            ctx, rows = self._context(dev, lay, static=True)
+            torch.cuda.current_stream(self.device).synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.caches, rows)
+            slot = _Graph(graph, dev, [host, torch.zeros_like(host).pin_memory()], [None, None],
+                          logits)
+            self._graphs[key] = slot
+        else:
+            i = slot.turn = 1 - slot.turn
+            if slot.copied[i] is not None:
+                slot.copied[i].synchronize()   # the copy that last read this buffer is done
+            self._fill(slot.hosts[i], lay)
+            slot.dev.copy_(slot.hosts[i], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            slot.copied[i] = ev
+        self.last_h2d_bytes = lay.total * 4
+        slot.graph.replay()
+        self.graph_replays += 1
+        return slot.logits
 
     # ------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """Run the batch; fp32 logits ``[wanted, vocab]`` on the device, or None."""
+        """Run the batch; fp32 logits ``[wanted, vocab]`` on the device, or None.
+
+        With graphs on, the logits of a replayed step live in the graph's own
+        buffer and are overwritten by the next step of the same shape."""
         fresh = self.manager.take_fresh_slots()
         if fresh:
             self.storage.zero_slots(fresh)
-        ctx, rows, R = self.build_context(entries)
-        logits = self.model.forward(ctx, self.caches, rows)
         self.steps_run += 1
-        return logits
+        if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
+            return self._graph_step(entries)
+        ctx, rows, _ = self.build_context(entries)
+        return self.model.forward(ctx, self.caches, rows)

@@ -73,12 +73,13 @@ class Runtime:
     """A loaded model with its cache and step function."""
 
     def __init__(self, model: DecoderModel, *, page_size: int = 16,
-                 num_pages: Union[int, Sequence[int]] = 256, max_slots: int = 8):
+                 num_pages: Union[int, Sequence[int]] = 256, max_slots: int = 8,
+                 use_graphs: bool = False):
         self.model = model
         needs = model.cache_needs()
         self.manager = CacheManager(groups_for(needs), num_pages, page_size, max_slots)
         self.storage = CacheStorage(needs, self.manager, model.ctx.dtype, model.ctx.device)
-        self.executor = Executor(model, self.manager, self.storage)
+        self.executor = Executor(model, self.manager, self.storage, use_graphs=use_graphs)
 
     @property
     def vocab_size(self) -> int:

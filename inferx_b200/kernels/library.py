@@ -138,6 +138,13 @@ def build(verbose: bool = True) -> str:
         tmp = out + f".tmp{os.getpid()}"
         _run([nvcc, "-shared", "-o", tmp] + objs, "link")
         os.replace(tmp, out)
+        for f in os.listdir(bdir):   # libraries of older sources
+            if f.startswith("libinferx_b200_") and f.endswith(".so") and \
+                    os.path.join(bdir, f) != out:
+                try:
+                    os.remove(os.path.join(bdir, f))
+                except OSError:
+                    pass
     finally:
         stop.set()
         for o in objs:
