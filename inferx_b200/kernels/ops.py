@@ -347,12 +347,57 @@ def append_kv(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: 
     _count()
 
 
+_DECODE_HEAD_SIZES = {torch.bfloat16: (64, 128, 256), torch.float32: (64, 128)}
+
+
+def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                           block_table: torch.Tensor, kv_len: torch.Tensor, max_kv_len: int,
+                           window: int, scale: float, splits: Optional[int] = None):
+    """Split-KV attention for a batch in which sequence s brings the one query q[s]
+    at position kv_len[s] - 1."""
+    _chk("q", q)
+    _chk("k_cache", k_cache, q.dtype)
+    _chk("v_cache", v_cache, q.dtype)
+    _chk("block_table", block_table, torch.int32)
+    _chk("kv_len", kv_len, torch.int32)
+    S, heads, hd = q.shape
+    P, kvh, page, chd = k_cache.shape
+    if chd != hd or v_cache.shape != k_cache.shape:
+        raise KernelError("paged_attention_decode: cache geometry differs from the query's")
+    if hd not in _DECODE_HEAD_SIZES.get(q.dtype, ()):
+        raise KernelError(f"paged_attention_decode: head size {hd} with {q.dtype} is not built; "
+                          "use the general kernel")
+    if kv_len.numel() != S or block_table.shape[0] != S:
+        raise KernelError("paged_attention_decode: one query per sequence is required")
+    lib = _lib()
+    if splits is None:
+        splits = lib.ix_attn_decode_splits(S, heads, kvh, int(max_kv_len))
+    out = torch.empty_like(q)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((S, heads, splits, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((S, heads, splits, 2), dtype=torch.float32, device=q.device)
+    code = lib.ix_paged_attention_decode(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
+        _ptr(part_ml), _ptr(out), _dtype_code(q), S, heads, kvh, hd, page, block_table.shape[1],
+        window, ctypes.c_float(scale), splits, _stream())
+    _check(code, "paged_attention_decode")
+    _count(2 if splits > 1 else 1)
+    return out
+
+
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, step, window: int, scale: float):
     """Causal attention of this step's queries over the paged cache.
 
     ``step`` carries the batch description (``seq_of_token``, ``positions``, ``cu_q``,
-    ``q_pos0``, ``kv_len``, ``max_q_len``, ``max_kv_len``, ``all_decode``)."""
+    ``q_pos0``, ``kv_len``, ``max_q_len``, ``max_kv_len``, ``all_decode``).  Steps of
+    single tokens go to the split-KV kernel; everything else, and head sizes the
+    tuned kernels do not take, to the general kernel."""
+    hd = q.shape[2]
+    if step.all_decode and hd in _DECODE_HEAD_SIZES.get(q.dtype, ()):
+        return paged_attention_decode(q, k_cache, v_cache, block_table, step.kv_len,
+                                      step.max_kv_len, window, scale)
     return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,
                                    step.positions, window, scale)
 

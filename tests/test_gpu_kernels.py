@@ -317,3 +317,42 @@ def test_cpu_tensor_is_refused():
         ops.silu_mul(torch.zeros(2, 4))
     with pytest.raises(ops.KernelError):
         ops.linear(torch.zeros(2, 4).cuda(), torch.zeros(3, 4).cuda().to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kvh,hd,page,window,splits", [
+    (4, 4, 128, 16, 0, None), (8, 2, 64, 8, 0, 3), (6, 3, 128, 16, 50, None),
+    (16, 2, 64, 4, 0, 1), (3, 1, 128, 16, 7, 5), (2, 2, 256, 16, 0, None)])
+def test_paged_attention_decode(dtype, heads, kvh, hd, page, window, splits):
+    ops = _ops()
+    if dtype == torch.float32 and hd == 256:
+        pytest.skip("fp32 decode kernel is built for head sizes 64 and 128")
+    seq_lens = [1, 37, 1000, 64, 513, 2]
+    q, kc, vc, bt, seq_of, pos = _paged_case(dtype, heads, kvh, hd, page, window, seq_lens,
+                                             [1] * len(seq_lens), seed=hd)
+    kv_len = torch.tensor(seq_lens, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(hd)
+    out = ops.paged_attention_decode(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), kv_len.cuda(),
+                                     max(seq_lens), window, scale, splits=splits)
+    ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, window, scale)
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **tol)
+
+
+def test_decode_attention_finds_one_far_key():
+    ops = _ops()
+    heads, kvh, hd, page = 4, 2, 128, 16
+    n = 3000
+    for far in (0, 15, 16, 255, 256, 1023, 1024, 2999):
+        q, kc, vc, bt, seq_of, pos = _paged_case(torch.bfloat16, heads, kvh, hd, page, 0, [n], [1],
+                                                 seed=far)
+        kc = kc * 0.01
+        key = torch.randn(hd)
+        kc[bt[0, far // page], :, far % page] = key.to(torch.bfloat16)
+        q[0, :, :] = (key * 2).to(torch.bfloat16)
+        vc[bt[0, far // page], :, far % page, 0] = 1000.0
+        out = ops.paged_attention_decode(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(),
+                                         torch.tensor([n], dtype=torch.int32).cuda(), n, 0, 1.0)
+        ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, 0, 1.0)
+        assert ref[0, 0, 0] > 900
+        torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=1.0)
