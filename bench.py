@@ -312,6 +312,77 @@ def time_e2e(cfg, batch, context, steps, warmup):
             "d2h_bytes_per_step": 4 * batch, "ms_per_step": dt / steps * 1e3}
 
 
+def breakdown(rt, batch, context, steps, prefill_tokens=0):
+    """Device time per kernel face over eager steps (CUDA events around every call of
+    the kernel module), as a table sorted by share.  A diagnostic, not a bench value."""
+    import torch
+    from inferx_b200.engine import StepEntry
+    from inferx_b200.kernels import ops
+    names = ["embed", "add_rmsnorm", "silu_mul", "linear", "gate_up_swiglu", "qkv_rope_append", "paged_attention",
+             "router_topk", "moe_dispatch", "grouped_gate_up_swiglu", "grouped_down",
+             "moe_combine", "sample"]
+    records, originals = [], {}
+
+    def wrap(name, fn):
+        def timed(*a, **k):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            out = fn(*a, **k)
+            e.record()
+            tag = name
+            if name == "linear":
+                tag = f"linear[{a[0].shape[0]}x{a[1].shape[0]}x{a[1].shape[1]}]"
+            records.append((tag, s, e))
+            return out
+        return timed
+
+    graphs, rt.executor.use_graphs = rt.executor.use_graphs, False
+    mgr = rt.manager
+    try:
+        if prefill_tokens:
+            for rid in list(mgr.live_requests()):
+                mgr.close(rid)
+        else:
+            fill_context(rt, batch, context)
+        g = torch.Generator().manual_seed(3)
+        for i in range(steps + 1):
+            if i == 1:
+                for n in names:
+                    originals[n] = getattr(ops, n)
+                    setattr(ops, n, wrap(n, originals[n]))
+            if prefill_tokens:
+                if mgr.has("p"):
+                    mgr.close("p")
+                mgr.open("p")
+                assert mgr.reserve("p", prefill_tokens)
+                toks = torch.randint(0, rt.vocab_size, (prefill_tokens,), generator=g).tolist()
+                logits = rt.executor.step([StepEntry("p", toks, [prefill_tokens - 1])])
+            else:
+                toks = torch.randint(0, rt.vocab_size, (batch,), generator=g).tolist()
+                for r in range(batch):
+                    assert mgr.reserve(r, mgr.length(r) + 1)
+                logits = rt.executor.step([StepEntry(r, [toks[r]], [0]) for r in range(batch)])
+                for r in range(batch):
+                    mgr.advance(r, 1)
+            ops.sample(logits)
+        torch.cuda.synchronize()
+    finally:
+        for n, fn in originals.items():
+            setattr(ops, n, fn)
+        rt.executor.use_graphs = graphs
+    totals = {}
+    for tag, s, e in records:
+        t = totals.setdefault(tag, [0.0, 0])
+        t[0] += s.elapsed_time(e)
+        t[1] += 1
+    whole = sum(v[0] for v in totals.values())
+    lines = [f"{'kernel face':44s} {'calls/step':>10s} {'ms/step':>9s} {'share':>7s}"]
+    for tag, (ms, n) in sorted(totals.items(), key=lambda kv: -kv[1][0]):
+        lines.append(f"{tag:44s} {n / steps:10.1f} {ms / steps:9.4f} {ms / whole:7.1%}")
+    lines.append(f"{'sum of device time':44s} {'':10s} {whole / steps:9.4f}")
+    return "\n".join(lines)
+
+
 def reference_arm():
     why = ("divedb/InferX is a C++20/CMake project with no Python package (no setup.py or "
            "pyproject.toml) and needs abseil, CLI11, folly and FlashInfer sources that are absent "
@@ -331,6 +402,8 @@ def main(argv=None):
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the default decode run")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--breakdown", choices=["decode", "prefill"],
+                    help="print device time per kernel face instead of the bench line")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm()
@@ -345,9 +418,13 @@ def main(argv=None):
     hbm_peak, tf_peak, peak_src = peaks()
     cfg = dict(A27B, num_hidden_layers=args.layers)
     B, C = args.batch, args.context
-    max_b = B if args.skip_points else max(B, 64)
+    max_b = B if (args.skip_points or args.breakdown) else max(B, 64)
     rt = make_runtime(cfg, max_b, C, args.steps + args.warmup + 8, use_graphs=not args.no_graphs)
 
+    if args.breakdown:
+        print(breakdown(rt, B, C, min(args.steps, 4),
+                        prefill_tokens=2048 if args.breakdown == "prefill" else 0))
+        return 0
     own, lib, touched = count_step_kernels(rt, B, C)
     clock = ClockSampler()
     dec = time_decode(rt, B, C, args.steps, args.warmup, sampler_clock=clock)

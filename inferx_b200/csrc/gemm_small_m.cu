@@ -1,0 +1,195 @@
+// Weight-streaming matrix product for few rows: y = x . w^T where every weight
+// matrix meets at most a few dozen activation rows (decode steps).  The work is
+// bandwidth: each weight element is read once, with 16-byte loads straight from
+// global memory into tensor-core fragments.
+//
+//   out[r, j] = sum_k x[src(r), k] * w[e(r), j, k]          (plain)
+//   out[r, j] = silu(x . wg[e, j]) * (x . wu[e, j])          (DUAL: SwiGLU fused)
+//
+// Groups are the experts of a mixture (ragged row ranges from `offsets`, source
+// rows from `rows`: the reference's GatherRows + GroupedGemmBf16Kernel<1> decode
+// variant + SiluMulFused, src/backends/cuda/ops/moe.cu:223-231,324-392,
+// src/backends/cuda/ops/layers.cu:512-529), or a single dense matrix with a few
+// rows (E = 1), where the reference calls cuBLASLt.
+//
+// Mapping: the product is computed transposed, out^T = w . x^T, with
+// mma.sync.m16n8k16: sixteen weight rows (output columns) are the M side, eight
+// activation rows the N side.  A thread's 16-byte load of a weight row holds eight
+// consecutive k; the same eight k of its activation row are loaded the same way,
+// and both are fed to the same k-slots of two mma instructions, so no shuffle or
+// shared-memory staging is needed (a dot product does not care in which order k is
+// visited, as long as both operands agree).  A block owns 16 output columns of one
+// group; its 8 warps split K and their partial sums are added through shared
+// memory in warp order, so a row's result does not depend on which other rows
+// share the tile.  Groups with more rows than one pass holds re-read their
+// weights (through L2).
+//
+// Requires bf16 inputs and K a multiple of 8 (16-byte chunks); refuses otherwise.
+#include "common.cuh"
+
+#define SM_THREADS 256
+#define SM_WARPS 8
+
+__device__ __forceinline__ uint4 ld_stream16(const bf16* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, unsigned a0, unsigned a1, unsigned a2,
+                                               unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename TO, bool DUAL, int NT>
+__global__ void __launch_bounds__(SM_THREADS)
+gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
+                    const int* __restrict__ offsets, const bf16* __restrict__ w,
+                    TO* __restrict__ out, int M_single, int N, int K, long long w_expert_stride) {
+  __shared__ float red[DUAL ? 2 : 1][SM_WARPS][NT][4][32];
+  const int e = blockIdx.y;
+  int lo, hi;
+  if (offsets) {
+    lo = offsets[e];
+    hi = offsets[e + 1];
+  } else {
+    lo = 0;
+    hi = M_single;
+  }
+  if (lo >= hi) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int j0 = blockIdx.x * 16;
+  const int ja = j0 + g, jb = j0 + g + 8;
+  const bool ja_ok = ja < N, jb_ok = jb < N;
+  const bf16* wbase = w + (size_t)e * w_expert_stride;
+  const bf16* wa = wbase + (size_t)(ja_ok ? ja : 0) * K;
+  const bf16* wb = wbase + (size_t)(jb_ok ? jb : 0) * K;
+  const bf16* ua = wa + (size_t)N * K;   // up rows follow the gate rows (DUAL)
+  const bf16* ub = wb + (size_t)N * K;
+  const int ksteps = (K + 31) >> 5;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+
+  for (int r0 = lo; r0 < hi; r0 += 8 * NT) {
+    const bf16* xrow[NT];
+    bool xok[NT];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      const int r = r0 + i * 8 + g;
+      xok[i] = r < hi;
+      const size_t src = xok[i] ? (rows ? (size_t)rows[r] : (size_t)r) : 0;
+      xrow[i] = x + src * K;
+    }
+    float acc[NT][4], acc2[DUAL ? NT : 1][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        acc[i][c] = 0.f;
+        if (DUAL) acc2[i][c] = 0.f;
+      }
+    constexpr int UNR = DUAL ? 4 : 8;
+    for (int s0 = warp; s0 < ksteps; s0 += SM_WARPS * UNR) {
+      uint4 va[UNR], vb[UNR], vua[DUAL ? UNR : 1], vub[DUAL ? UNR : 1];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int kb = (s0 + u * SM_WARPS) * 32 + t * 8;
+        const bool kok = kb < K;
+        va[u] = (kok && ja_ok) ? ld_stream16(wa + kb) : zero;
+        vb[u] = (kok && jb_ok) ? ld_stream16(wb + kb) : zero;
+        if (DUAL) {
+          vua[u] = (kok && ja_ok) ? ld_stream16(ua + kb) : zero;
+          vub[u] = (kok && jb_ok) ? ld_stream16(ub + kb) : zero;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int kb = (s0 + u * SM_WARPS) * 32 + t * 8;
+        const bool kok = kb < K;
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+          uint4 xv = zero;
+          if (kok && xok[i]) xv = *reinterpret_cast<const uint4*>(xrow[i] + kb);
+          mma_bf16_16816(acc[i], va[u].x, vb[u].x, va[u].y, vb[u].y, xv.x, xv.y);
+          mma_bf16_16816(acc[i], va[u].z, vb[u].z, va[u].w, vb[u].w, xv.z, xv.w);
+          if (DUAL) {
+            mma_bf16_16816(acc2[i], vua[u].x, vub[u].x, vua[u].y, vub[u].y, xv.x, xv.y);
+            mma_bf16_16816(acc2[i], vua[u].z, vub[u].z, vua[u].w, vub[u].w, xv.z, xv.w);
+          }
+        }
+      }
+    }
+    __syncthreads();   // the previous pass has read its sums
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        red[0][warp][i][c][lane] = acc[i][c];
+        if (DUAL) red[1][warp][i][c][lane] = acc2[i][c];
+      }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < NT * 128; idx += SM_THREADS) {
+      const int l = idx & 31, c = (idx >> 5) & 3, i = idx >> 7;
+      float v = 0.f, v2 = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < SM_WARPS; ++wq) {
+        v += red[0][wq][i][c][l];
+        if (DUAL) v2 += red[1][wq][i][c][l];
+      }
+      const int gg = l >> 2, tt = l & 3;
+      const int j = j0 + ((c & 2) ? gg + 8 : gg);
+      const int r = r0 + i * 8 + 2 * tt + (c & 1);
+      if (j < N && r < hi) {
+        if (DUAL) v = v / (1.0f + __expf(-v)) * v2;
+        out[(size_t)r * N + j] = from_f32<TO>(v);
+      }
+    }
+  }
+}
+
+template <typename TO, bool DUAL, int NT>
+static int launch_small_m(const void* x, const int* rows, const int* offsets, const void* w,
+                          void* out, int M, int N, int K, int E, cudaStream_t stream) {
+  if (E > 65535) return IX_ERR_SIZE;
+  const long long w_rows = DUAL ? 2LL * N : N;
+  dim3 grid((N + 15) / 16, E);
+  gemm_small_m_kernel<TO, DUAL, NT><<<grid, SM_THREADS, 0, stream>>>(
+      (const bf16*)x, rows, offsets, (const bf16*)w, (TO*)out, offsets ? 0 : M, N, K, w_rows * K);
+  return ix_launch_status();
+}
+
+// x: [*, K] bf16; w: [E, N (or 2N when dual), K] bf16; out: [rows, N] bf16 or fp32.
+// offsets == null: one matrix (E must be 1) with M rows.  rows_per_pass: 8, 16 or 32
+// activation rows handled per pass over a group's weights.
+IX_API int ix_gemm_small_m(const void* x, const int* rows, const int* offsets, const void* w,
+                           void* out, int out_dtype, int dual, int M, int N, int K, int E,
+                           int rows_per_pass, cudaStream_t stream) {
+  if (N <= 0 || K <= 0 || E <= 0) return IX_ERR_SIZE;
+  if (K % 8 != 0) return IX_ERR_UNSUPPORTED;
+  if (!offsets && E != 1) return IX_ERR_SIZE;
+  if (!offsets && M <= 0) return IX_OK;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return IX_ERR_ALIGN;
+  const int nt = rows_per_pass > 16 ? 4 : (rows_per_pass > 8 ? 2 : 1);
+#define IX_SM(TO, D)                                                                          \
+  do {                                                                                        \
+    if (nt == 4) return launch_small_m<TO, D, 4>(x, rows, offsets, w, out, M, N, K, E, stream); \
+    if (nt == 2) return launch_small_m<TO, D, 2>(x, rows, offsets, w, out, M, N, K, E, stream); \
+    return launch_small_m<TO, D, 1>(x, rows, offsets, w, out, M, N, K, E, stream);             \
+  } while (0)
+  if (out_dtype == IX_BF16) {
+    if (dual) IX_SM(bf16, true);
+    IX_SM(bf16, false);
+  }
+  if (out_dtype == IX_F32) {
+    if (dual) IX_SM(float, true);
+    IX_SM(float, false);
+  }
+#undef IX_SM
+  return IX_ERR_DTYPE;
+}

@@ -19,6 +19,53 @@
 #define ROUTER_MAX_TOK 8
 #define ROUTER_MAX_TOPK 32
 
+// Softmax over p[0..E) (logits, overwritten), then k rounds of masked argmax by one
+// warp; ties go to the lower index.  Writes k weights and k expert ids.
+__device__ __forceinline__ void select_topk(float* p, int E, int k, int renorm, float scale,
+                                            float* __restrict__ out_w, int* __restrict__ out_i,
+                                            int lane) {
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, p[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float v = expf(p[e] - mx);
+    p[e] = v;
+    sum += v;
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  float total = 0.f;
+  float my_w = 0.f;  // lane s keeps slot s
+  int my_i = 0;
+  for (int s = 0; s < k; ++s) {
+    float best = -1.f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = p[e];
+      if (v > best) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    const float prob = best / sum;
+    if (lane == s) { my_w = prob; my_i = bi; }
+    total += prob;
+    if (lane == 0) p[bi] = -2.f;  // masked: below every probability
+    __syncwarp();
+  }
+  if (lane < k) {
+    float wv = my_w;
+    if (renorm && total > 0.f) wv = wv / total;
+    wv *= scale;
+    out_w[lane] = wv;
+    out_i[lane] = my_i;
+  }
+}
+
 template <typename TA, int TOK>
 __global__ void __launch_bounds__(ROUTER_THREADS)
 router_topk_kernel(const TA* __restrict__ x, const float* __restrict__ w,
@@ -62,47 +109,8 @@ router_topk_kernel(const TA* __restrict__ x, const float* __restrict__ w,
   for (int tk = warp; tk < TOK; tk += nwarps) {
     const int t = t0 + tk;
     if (t >= T) continue;
-    float* p = lg + tk * E;
-    float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, p[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) {
-      const float v = expf(p[e] - mx);
-      p[e] = v;
-      sum += v;
-    }
-    sum = warp_sum(sum);
-    __syncwarp();
-    float total = 0.f;
-    float my_w = 0.f;  // lane s keeps slot s
-    int my_i = 0;
-    for (int s = 0; s < k; ++s) {
-      float best = -1.f;
-      int bi = 0x7fffffff;
-      for (int e = lane; e < E; e += 32) {
-        const float v = p[e];
-        if (v > best) { best = v; bi = e; }
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-      }
-      const float prob = best / sum;
-      if (lane == s) { my_w = prob; my_i = bi; }
-      total += prob;
-      if (lane == 0) p[bi] = -2.f;  // masked: below every probability
-      __syncwarp();
-    }
-    if (lane < k) {
-      float wv = my_w;
-      if (renorm && total > 0.f) wv = wv / total;
-      wv *= scale;
-      topk_w[(size_t)t * k + lane] = wv;
-      topk_idx[(size_t)t * k + lane] = my_i;
-    }
+    select_topk(lg + tk * E, E, k, renorm, scale, topk_w + (size_t)t * k, topk_idx + (size_t)t * k,
+                lane);
   }
 }
 
@@ -124,12 +132,61 @@ static int launch_router(const void* x, const float* w, const float* extra_w, in
   return ix_launch_status();
 }
 
+// Few tokens: one warp per (token, expert) for the logits, so that the router
+// weights are streamed by many blocks at once, then one warp per token selects.
+// The dot product uses the same lane striding and shuffle tree as the fused
+// kernel, so a token's routing does not depend on which path ran.
+template <typename TA>
+__global__ void __launch_bounds__(ROUTER_THREADS)
+router_logits_kernel(const TA* __restrict__ x, const float* __restrict__ w,
+                     const float* __restrict__ extra_w, int T, int H, int E,
+                     float* __restrict__ logits, float* __restrict__ extra_out) {
+  const int lane = threadIdx.x & 31;
+  const int pair = blockIdx.x * (ROUTER_THREADS / 32) + (threadIdx.x >> 5);
+  const int rows_total = E + (extra_w ? 1 : 0);
+  if (pair >= T * rows_total) return;
+  const int t = pair / rows_total, e = pair - t * rows_total;
+  const float* wr = e < E ? w + (size_t)e * H : extra_w;
+  const TA* xr = x + (size_t)t * H;
+  float acc = 0.f;
+  for (int i = lane; i < H; i += 32) acc += to_f32(xr[i]) * wr[i];
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    if (e < E) logits[(size_t)t * E + e] = acc;
+    else extra_out[t] = acc;
+  }
+}
+
+__global__ void __launch_bounds__(32)
+router_select_kernel(const float* __restrict__ logits, int E, int k, int renorm, float scale,
+                     float* __restrict__ topk_w, int* __restrict__ topk_idx) {
+  extern __shared__ float prob[];
+  const int t = blockIdx.x, lane = threadIdx.x;
+  for (int e = lane; e < E; e += 32) prob[e] = logits[(size_t)t * E + e];
+  __syncwarp();
+  select_topk(prob, E, k, renorm, scale, topk_w + (size_t)t * k, topk_idx + (size_t)t * k, lane);
+}
+
 IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, int act_dtype,
                           int T, int H, int E, int k, int renorm, float scale, float* topk_w,
-                          int* topk_idx, float* extra_out, cudaStream_t stream) {
+                          int* topk_idx, float* extra_out, float* logits_scratch,
+                          cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (H <= 0 || E <= 0 || k <= 0 || k > E || k > ROUTER_MAX_TOPK) return IX_ERR_SIZE;
   if (extra_w && !extra_out) return IX_ERR_SIZE;
+  if (logits_scratch && T < 2 * 148 && (size_t)E * sizeof(float) <= 48 * 1024) {
+    // logits_scratch: [T, E] fp32
+    const long long pairs = (long long)T * (E + (extra_w ? 1 : 0));
+    const int blocks = (int)((pairs + ROUTER_THREADS / 32 - 1) / (ROUTER_THREADS / 32));
+    IX_DISPATCH_DTYPE(act_dtype, TA,
+                      (router_logits_kernel<TA><<<blocks, ROUTER_THREADS, 0, stream>>>(
+                          (const TA*)x, w, extra_w, T, H, E, logits_scratch, extra_out)));
+    int rc = ix_launch_status();
+    if (rc != 0) return rc;
+    router_select_kernel<<<T, 32, (size_t)E * sizeof(float), stream>>>(
+        logits_scratch, E, k, renorm, scale, topk_w, topk_idx);
+    return ix_launch_status();
+  }
   // many tokens share one pass over the router weights; few tokens spread out
   const size_t per_tok = ((size_t)H + E) * sizeof(float);
   int tok = T >= 8 * 148 ? 8 : (T >= 2 * 148 ? 2 : 1);

@@ -152,6 +152,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if K != K2:
         raise KernelError(f"linear: inner sizes differ ({K} vs {K2})")
     out_dtype = out_dtype or x.dtype
+    if M <= SMALL_M_DENSE_ROWS and _streams_weights(x, w):
+        return gemm_small_m(x, w.unsqueeze(0), None, None, False, M, out_dtype=out_dtype,
+                            rows_per_pass=M)
     if x.dtype == torch.bfloat16:
         LIBRARY_CALLS[0] += 1
         if out_dtype == torch.bfloat16:
@@ -270,11 +273,13 @@ def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, renormalize: bool,
     tw = torch.empty((T, top_k), dtype=torch.float32, device=x.device)
     ti = torch.empty((T, top_k), dtype=torch.int32, device=x.device)
     ex = torch.empty((T,), dtype=torch.float32, device=x.device) if extra_w is not None else None
+    few = T < 2 * 148   # few tokens: logits by many blocks, then a selection kernel
+    scratch = torch.empty((T, E), dtype=torch.float32, device=x.device) if few else None
     code = _lib().ix_router_topk(_ptr(x), _ptr(w), _ptr(extra_w), _dtype_code(x), T, H, E, top_k,
                                  1 if renormalize else 0, ctypes.c_float(scale), _ptr(tw),
-                                 _ptr(ti), _ptr(ex), _stream())
+                                 _ptr(ti), _ptr(ex), _ptr(scratch), _stream())
     _check(code, "router_topk")
-    _count()
+    _count(2 if few else 1)
     return tw, ti, ex
 
 
@@ -402,14 +407,66 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                                    step.positions, window, scale)
 
 
+SMALL_M_ROWS_PER_GROUP = 8   # grouped: up to this many rows per expert on average
+SMALL_M_DENSE_ROWS = 32      # dense: up to this many rows stream the weights once
+
+
+def gemm_small_m(x: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor],
+                 offsets: Optional[torch.Tensor], dual: bool, num_out_rows: int,
+                 out_dtype: Optional[torch.dtype] = None, rows_per_pass: int = 8):
+    """Weight-streaming product for few rows per weight matrix (bf16 inputs)."""
+    _chk("x", x, torch.bfloat16)
+    _chk("w", w, torch.bfloat16)
+    _chk("rows", rows, torch.int32, optional=True)
+    _chk("offsets", offsets, torch.int32, optional=True)
+    E, w_rows, K = w.shape
+    N = w_rows // 2 if dual else w_rows
+    if x.shape[1] != K:
+        raise KernelError(f"gemm_small_m: inner sizes differ ({x.shape[1]} vs {K})")
+    out_dtype = out_dtype or x.dtype
+    out = torch.empty((num_out_rows, N), dtype=out_dtype, device=x.device)
+    code = _lib().ix_gemm_small_m(
+        _ptr(x), _ptr(rows), _ptr(offsets), _ptr(w), _ptr(out),
+        F32 if out_dtype == torch.float32 else BF16, 1 if dual else 0,
+        0 if offsets is not None else x.shape[0], N, K, E, rows_per_pass, _stream())
+    _check(code, "gemm_small_m")
+    _count()
+    return out
+
+
+def _streams_weights(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the weight-streaming kernel takes these operands: bf16, K in 16-byte chunks."""
+    return x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[-1] % 8 == 0
+
+
 def grouped_gate_up_swiglu(x: torch.Tensor, rows: torch.Tensor, offsets: torch.Tensor,
                            w_gate_up: torch.Tensor):
     """act[r] = silu(x[rows[r]] . Wg[e]^T) * (x[rows[r]] . Wu[e]^T), e from offsets.
 
     ``w_gate_up``: [E, 2I, H], per expert the gate rows then the up rows."""
-    return gemm_generic(x, w_gate_up, rows, offsets, dual=True, num_out_rows=rows.numel())
+    A = rows.numel()
+    per = A / w_gate_up.shape[0]
+    if per <= SMALL_M_ROWS_PER_GROUP and _streams_weights(x, w_gate_up):
+        return gemm_small_m(x, w_gate_up, rows, offsets, True, A,
+                            rows_per_pass=8 if per <= 2 else 16)
+    return gemm_generic(x, w_gate_up, rows, offsets, dual=True, num_out_rows=A)
 
 
 def grouped_down(act: torch.Tensor, offsets: torch.Tensor, w_down: torch.Tensor):
     """y[r] = act[r] . Wd[e]^T with ``w_down`` [E, H, I]."""
-    return gemm_generic(act, w_down, None, offsets, dual=False, num_out_rows=act.shape[0])
+    A = act.shape[0]
+    per = A / w_down.shape[0]
+    if per <= SMALL_M_ROWS_PER_GROUP and _streams_weights(act, w_down):
+        return gemm_small_m(act, w_down, None, offsets, False, A,
+                            rows_per_pass=8 if per <= 2 else 16)
+    return gemm_generic(act, w_down, None, offsets, dual=False, num_out_rows=A)
+
+
+def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor):
+    """Dense SwiGLU front half: silu(x . Wg^T) * (x . Wu^T) with ``w_gate_up`` [2I, H]."""
+    _chk("x", x)
+    _chk("w_gate_up", w_gate_up, x.dtype)
+    M = x.shape[0]
+    if M <= SMALL_M_DENSE_ROWS and _streams_weights(x, w_gate_up):
+        return gemm_small_m(x, w_gate_up.unsqueeze(0), None, None, True, M, rows_per_pass=M)
+    return silu_mul(linear(x, w_gate_up))

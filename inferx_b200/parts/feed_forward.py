@@ -41,8 +41,7 @@ class SwiGluFeedForward:
 
     def forward(self, x, step=None):
         ops = self.ctx.ops
-        act = ops.silu_mul(ops.linear(x, self.gate_up_w))
-        return ops.linear(act, self.down_w)
+        return ops.linear(ops.gate_up_swiglu(x, self.gate_up_w), self.down_w)
 
 
 class MoeFeedForward:

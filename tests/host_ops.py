@@ -47,6 +47,10 @@ def linear(x, w, out_dtype=None):
     return (_f(x) @ _f(w).T).to(out_dtype or x.dtype)
 
 
+def gate_up_swiglu(x, w_gate_up):
+    return silu_mul(linear(x, w_gate_up))
+
+
 def _rotate(x, positions, inv_freq, rot):
     # x [T, heads, hd] fp32
     if not rot:

@@ -356,3 +356,63 @@ def test_decode_attention_finds_one_far_key():
         ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, 0, 1.0)
         assert ref[0, 0, 0] > 900
         torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=1.0)
+
+
+@pytest.mark.parametrize("T,H,I,E,k", [(1, 64, 32, 4, 2), (9, 200, 72, 8, 3), (40, 96, 48, 60, 4),
+                                       (16, 2048, 1408, 6, 2)])
+def test_small_m_grouped_experts(T, H, I, E, k):
+    """The weight-streaming kernel (few rows per expert) against the plain statement,
+    including an expert with more rows than one chunk holds."""
+    ops = _ops()
+    dtype = torch.bfloat16
+    x = _rand((T, H), dtype, seed=21)
+    wgu = _rand((E, 2 * I, H), dtype, 0.1, seed=22)
+    wd = _rand((E, H, I), dtype, 0.1, seed=23)
+    g = torch.Generator().manual_seed(24)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    if T >= 9:
+        idx[:, 0] = 1          # one expert gets every token: more rows than a chunk
+        idx[:, 1:] = torch.where(idx[:, 1:] == 1, torch.zeros_like(idx[:, 1:]), idx[:, 1:])
+        for t in range(T):     # keep the k experts of a token distinct
+            seen, row = set(), idx[t].tolist()
+            for j, e in enumerate(row):
+                while e in seen:
+                    e = (e + 1) % E
+                seen.add(e)
+                row[j] = e
+            idx[t] = torch.tensor(row, dtype=torch.int32)
+    off, rows, dest = host_ops.moe_dispatch(idx, E)
+    act = ops.gemm_small_m(x.cuda(), wgu.cuda(), rows.cuda(), off.cuda(), True, rows.numel())
+    ract = host_ops.grouped_gate_up_swiglu(x, rows, off, wgu)
+    torch.testing.assert_close(act.cpu().float(), ract.float(), **_tol(dtype))
+    y = ops.gemm_small_m(ract.cuda(), wd.cuda(), None, off.cuda(), False, ract.shape[0])
+    ry = host_ops.grouped_down(ract, off, wd)
+    torch.testing.assert_close(y.cpu().float(), ry.float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 50, 72), (8, 130, 200), (13, 64, 256), (16, 1000, 2048),
+                                   (3, 300, 5632), (29, 90, 1408), (32, 48, 40)])
+def test_small_m_dense(M, N, K):
+    ops = _ops()
+    dtype = torch.bfloat16
+    x, w = _rand((M, K), dtype, seed=31), _rand((N, K), dtype, 0.1, seed=32)
+    out = ops.linear(x.cuda(), w.cuda())
+    torch.testing.assert_close(out.cpu().float(), host_ops.linear(x, w).float(), **_tol(dtype))
+    out32 = ops.linear(x.cuda(), w.cuda(), out_dtype=torch.float32)
+    torch.testing.assert_close(out32.cpu(), host_ops.linear(x, w, torch.float32),
+                               rtol=1e-3, atol=1e-3)
+    if N % 2 == 0:
+        act = ops.gate_up_swiglu(x.cuda(), w.cuda())
+        torch.testing.assert_close(act.cpu().float(), host_ops.gate_up_swiglu(x, w).float(),
+                                   **_tol(dtype))
+
+
+def test_router_paths_agree_bitwise():
+    """Few tokens take the two-kernel router, many the fused one: same routing, same bits."""
+    ops = _ops()
+    x = _rand((600, 256), torch.bfloat16, seed=41).cuda()
+    w = _rand((60, 256), torch.float32, 0.3, seed=42).cuda()
+    extra = _rand((256,), torch.float32, 0.3, seed=43).cuda()
+    tw, ti, ex = ops.router_topk(x, w, 4, False, 1.0, extra_w=extra)
+    tw2, ti2, ex2 = ops.router_topk(x[:40].contiguous(), w, 4, False, 1.0, extra_w=extra)
+    assert torch.equal(ti[:40], ti2) and torch.equal(tw[:40], tw2) and torch.equal(ex[:40], ex2)
