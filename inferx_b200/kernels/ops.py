@@ -391,6 +391,40 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     return out
 
 
+_PREFILL_HEAD_SIZES = {torch.bfloat16: (64, 128)}
+
+
+def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                            block_table: torch.Tensor, cu_q: torch.Tensor, q_pos0: torch.Tensor,
+                            window: int, scale: float):
+    """Tensor-core attention for a ragged batch: sequence s brings the queries
+    q[cu_q[s]:cu_q[s+1]] at positions q_pos0[s], q_pos0[s]+1, ..."""
+    _chk("q", q, torch.bfloat16)
+    _chk("k_cache", k_cache, q.dtype)
+    _chk("v_cache", v_cache, q.dtype)
+    _chk("block_table", block_table, torch.int32)
+    _chk("cu_q", cu_q, torch.int32)
+    _chk("q_pos0", q_pos0, torch.int32)
+    T, heads, hd = q.shape
+    P, kvh, page, chd = k_cache.shape
+    S = q_pos0.numel()
+    if chd != hd or v_cache.shape != k_cache.shape:
+        raise KernelError("paged_attention_prefill: cache geometry differs from the query's")
+    if hd not in _PREFILL_HEAD_SIZES.get(q.dtype, ()):
+        raise KernelError(f"paged_attention_prefill: head size {hd} is not built; use the "
+                          "general kernel")
+    if cu_q.numel() != S + 1 or block_table.shape[0] != S:
+        raise KernelError("paged_attention_prefill: cu_q, q_pos0 and block_table disagree")
+    out = torch.empty_like(q)
+    code = _lib().ix_paged_attention_prefill(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(cu_q), _ptr(q_pos0),
+        _ptr(out), _dtype_code(q), T, S, heads, kvh, hd, page, block_table.shape[1], window,
+        ctypes.c_float(scale), _stream())
+    _check(code, "paged_attention_prefill")
+    _count()
+    return out
+
+
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, step, window: int, scale: float):
     """Causal attention of this step's queries over the paged cache.
@@ -403,6 +437,9 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     if step.all_decode and hd in _DECODE_HEAD_SIZES.get(q.dtype, ()):
         return paged_attention_decode(q, k_cache, v_cache, block_table, step.kv_len,
                                       step.max_kv_len, window, scale)
+    if hd in _PREFILL_HEAD_SIZES.get(q.dtype, ()):
+        return paged_attention_prefill(q, k_cache, v_cache, block_table, step.cu_q, step.q_pos0,
+                                       window, scale)
     return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,
                                    step.positions, window, scale)
 

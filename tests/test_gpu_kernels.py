@@ -416,3 +416,50 @@ def test_router_paths_agree_bitwise():
     tw, ti, ex = ops.router_topk(x, w, 4, False, 1.0, extra_w=extra)
     tw2, ti2, ex2 = ops.router_topk(x[:40].contiguous(), w, 4, False, 1.0, extra_w=extra)
     assert torch.equal(ti[:40], ti2) and torch.equal(tw[:40], tw2) and torch.equal(ex[:40], ex2)
+
+
+@pytest.mark.parametrize("heads,kvh,hd,page,window", [
+    (4, 2, 128, 16, 0), (3, 1, 64, 8, 0), (2, 2, 128, 4, 40), (6, 3, 64, 16, 7),
+    (2, 1, 128, 16, 100)])
+def test_paged_attention_prefill(heads, kvh, hd, page, window):
+    """Ragged batch: whole prompts, a portion deep in a sequence, single tokens."""
+    ops = _ops()
+    dtype = torch.bfloat16
+    seq_lens, q_lens = [150, 1, 333, 64, 65, 700], [150, 1, 70, 64, 2, 1]
+    q, kc, vc, bt, seq_of, pos = _paged_case(dtype, heads, kvh, hd, page, window, seq_lens, q_lens,
+                                             seed=hd + window)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    cu_q = torch.tensor(cu, dtype=torch.int32)
+    q_pos0 = torch.tensor([n - ql for n, ql in zip(seq_lens, q_lens)], dtype=torch.int32)
+    scale = 1.0 / math.sqrt(hd)
+    out = ops.paged_attention_prefill(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cu_q.cuda(),
+                                      q_pos0.cuda(), window, scale)
+    ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, window, scale)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_prefill_attention_window_edge_and_far_key():
+    """A marked key just inside / just outside the window of one query in a long
+    portion, and a far key without a window."""
+    ops = _ops()
+    heads, kvh, hd, page = 1, 1, 64, 16
+    n, ql = 300, 130
+    for window, which, qrow, expect in ((50, 299 - 49 - 20, 129 - 20, True),
+                                        (50, 299 - 50 - 20, 129 - 20, False),
+                                        (0, 3, 129, True), (0, 64, 0, True), (0, 171, 0, False)):
+        q, kc, vc, bt, seq_of, pos = _paged_case(torch.bfloat16, heads, kvh, hd, page, window, [n],
+                                                 [ql], seed=which)
+        kc = kc * 0.01
+        vc = vc * 0.0
+        key = torch.ones(hd)
+        kc[bt[0, which // page], 0, which % page] = (key * 4).to(torch.bfloat16)
+        vc[bt[0, which // page], 0, which % page, 0] = 1.0
+        q = q * 0.01
+        q[qrow, 0] = (key * 4).to(torch.bfloat16)
+        cu_q = torch.tensor([0, ql], dtype=torch.int32)
+        q_pos0 = torch.tensor([n - ql], dtype=torch.int32)
+        out = ops.paged_attention_prefill(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cu_q.cuda(),
+                                          q_pos0.cuda(), window, 1.0)
+        assert (out[qrow, 0, 0].item() > 0.9) == expect, (window, which, qrow)
