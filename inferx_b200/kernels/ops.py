@@ -444,6 +444,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                                    step.positions, window, scale)
 
 
+USE_TCGEN05 = True           # prompt-sized grouped products go to the tcgen05 kernel
 SMALL_M_ROWS_PER_GROUP = 8   # grouped: up to this many rows per expert on average
 SMALL_M_DENSE_ROWS = 32      # dense: up to this many rows stream the weights once
 
@@ -471,6 +472,60 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor],
     return out
 
 
+def gather_rows(x: torch.Tensor, rows: torch.Tensor):
+    """out[i] = x[rows[i]] with 16-byte copies (row size must be a multiple of 16 bytes)."""
+    _chk("x", x)
+    _chk("rows", rows, torch.int32)
+    n = rows.numel()
+    out = torch.empty((n, x.shape[1]), dtype=x.dtype, device=x.device)
+    _check(_lib().ix_gather_rows(_ptr(x), _ptr(rows), _ptr(out), n,
+                                 x.shape[1] * x.element_size(), _stream()), "gather_rows")
+    _count()
+    return out
+
+
+_TC_STATUS = {}
+
+
+def _tc_status(device) -> torch.Tensor:
+    key = torch.device(device).index or 0
+    if key not in _TC_STATUS:
+        _TC_STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _TC_STATUS[key]
+
+
+def check_async_errors():
+    """Raise if a tensor-core kernel gave up on one of its bounded waits.  Reads a
+    status word from the device, so it synchronises; call it where the host waits
+    for results anyway."""
+    for key, st in _TC_STATUS.items():
+        code = int(st.item())
+        if code:
+            st.zero_()
+            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, "?")
+            raise KernelError(f"grouped_gemm_tc on cuda:{key}: {role} waited past its limit "
+                              f"(status {code}); the output of that call is not valid")
+
+
+def grouped_gemm_tc(a: torch.Tensor, offsets: torch.Tensor, w: torch.Tensor, dual: bool):
+    """Grouped product on tcgen05 tensor cores: ``a`` [rows, K] already grouped by
+    expert, ``w`` [E, N or 2N, K]; returns [rows, N] bf16."""
+    _chk("a", a, torch.bfloat16)
+    _chk("w", w, torch.bfloat16)
+    _chk("offsets", offsets, torch.int32)
+    E, w_rows, K = w.shape
+    N = w_rows // 2 if dual else w_rows
+    if a.shape[1] != K:
+        raise KernelError(f"grouped_gemm_tc: inner sizes differ ({a.shape[1]} vs {K})")
+    out = torch.empty((a.shape[0], N), dtype=torch.bfloat16, device=a.device)
+    code = _lib().ix_grouped_gemm_tc(_ptr(a), _ptr(offsets), _ptr(w), _ptr(out),
+                                     1 if dual else 0, a.shape[0], N, K, E,
+                                     _ptr(_tc_status(a.device)), _stream())
+    _check(code, "grouped_gemm_tc")
+    _count()
+    return out
+
+
 def _streams_weights(x: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether the weight-streaming kernel takes these operands: bf16, K in 16-byte chunks."""
     return x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[-1] % 8 == 0
@@ -486,6 +541,8 @@ def grouped_gate_up_swiglu(x: torch.Tensor, rows: torch.Tensor, offsets: torch.T
     if per <= SMALL_M_ROWS_PER_GROUP and _streams_weights(x, w_gate_up):
         return gemm_small_m(x, w_gate_up, rows, offsets, True, A,
                             rows_per_pass=8 if per <= 2 else 16)
+    if USE_TCGEN05 and _streams_weights(x, w_gate_up):
+        return grouped_gemm_tc(gather_rows(x, rows), offsets, w_gate_up, True)
     return gemm_generic(x, w_gate_up, rows, offsets, dual=True, num_out_rows=A)
 
 
@@ -496,6 +553,8 @@ def grouped_down(act: torch.Tensor, offsets: torch.Tensor, w_down: torch.Tensor)
     if per <= SMALL_M_ROWS_PER_GROUP and _streams_weights(act, w_down):
         return gemm_small_m(act, w_down, None, offsets, False, A,
                             rows_per_pass=8 if per <= 2 else 16)
+    if USE_TCGEN05 and _streams_weights(act, w_down):
+        return grouped_gemm_tc(act, offsets, w_down, False)
     return gemm_generic(act, w_down, None, offsets, dual=False, num_out_rows=A)
 
 
