@@ -1,0 +1,115 @@
+"""Typed configuration and the architecture registry (behaviours of the reference's
+tests/unit/config_test.cc:152-201 plus the keys the reference does not read)."""
+import json
+
+import pytest
+
+from conftest import TINY_A, TINY_B
+from inferx_b200.config import (ConfigError, Qwen2MoeConfig, config_from_dir, config_from_json,
+                                known_architectures, register_architecture)
+from inferx_b200.config import registry as reg
+
+
+def test_parses_a_qwen2_moe_checkpoint_config():
+    cfg, spec = config_from_json({
+        "architectures": ["Qwen2MoeForCausalLM"], "hidden_size": 2048, "intermediate_size": 5632,
+        "num_hidden_layers": 24, "num_attention_heads": 16, "num_key_value_heads": 16,
+        "vocab_size": 151936, "num_experts": 60, "num_experts_per_tok": 4,
+        "moe_intermediate_size": 1408, "norm_topk_prob": False,
+        "shared_expert_intermediate_size": 5632})
+    assert isinstance(cfg, Qwen2MoeConfig)
+    assert (cfg.num_experts, cfg.num_experts_per_tok, cfg.moe_intermediate_size) == (60, 4, 1408)
+    assert cfg.shared_expert_intermediate_size == 5632 and cfg.intermediate_size == 5632
+    assert cfg.norm_topk_prob is False
+    assert cfg.head_dim == 128 and cfg.attention_bias is True
+    assert cfg.rms_norm_eps == 1e-6 and cfg.rope_theta == 10000.0
+    assert len(spec.layers) == 24 and all(l.ffn.kind == "moe" for l in spec.layers)
+    assert all(l.mixer.window == 0 for l in spec.layers)
+
+
+def test_per_layer_choices_follow_the_config(tiny_a, tiny_b):
+    _, a = config_from_json(tiny_a)
+    assert [l.ffn.kind for l in a.layers] == ["moe", "moe"]
+    assert a.layers[0].ffn.renormalize is True and a.tied_head is False
+    cfg, b = config_from_json(tiny_b)
+    # mlp_only_layers [0], decoder_sparse_step 2 -> only layer 1 is sparse
+    assert [l.ffn.kind for l in b.layers] == ["swiglu", "moe", "swiglu"]
+    assert b.layers[0].ffn.intermediate == 128
+    # sliding window on layers >= max_window_layers (1)
+    assert [l.mixer.window for l in b.layers] == [0, 8, 8]
+    assert b.layers[1].ffn.top_k == 3 and b.layers[1].ffn.renormalize is False
+    assert b.tied_head is True and b.layers[0].mixer.kv_heads == 1
+    assert b.layers[0].mixer.position.theta == 1e6 and b.layers[0].input_norm.eps == 1e-5
+
+
+@pytest.mark.parametrize("change,match", [
+    ({"num_experts_per_tok": 8}, "exceeds num_experts"),
+    ({"num_experts_per_tok": None}, "num_experts_per_tok"),
+    ({"num_attention_heads": 3}, "multiple of"),
+    ({"head_dim": 15}, "even"),
+    ({"hidden_size": "64"}, "must be an integer"),
+    ({"norm_topk_prob": 1}, "true or false"),
+    ({"vocab_size": None}, "required key 'vocab_size'"),
+    ({"decoder_sparse_step": 0}, "at least 1"),
+    ({"mlp_only_layers": [0, 1]}, "no layer is sparse"),
+    ({"mlp_only_layers": [0]}, "intermediate_size"),
+    ({"mlp_only_layers": [7]}, "not a layer"),
+    ({"use_sliding_window": True}, "sliding_window"),
+    ({"rope_scaling": {"type": "yarn"}}, "rope_scaling"),
+    ({"torch_dtype": "int8"}, "torch_dtype"),
+    ({"architectures": ["Qwen2MoeForCausalLM", "X"]}, "exactly one"),
+])
+def test_rejections(tiny_a, change, match):
+    cfg = dict(tiny_a)
+    for k, v in change.items():
+        if v is None:
+            cfg.pop(k, None)
+        else:
+            cfg[k] = v
+    with pytest.raises(ConfigError, match=match):
+        config_from_json(cfg)
+
+
+def test_unknown_architecture_lists_the_known_ones(tiny_a):
+    with pytest.raises(ConfigError, match="Qwen2MoeForCausalLM"):
+        config_from_json(dict(tiny_a, architectures=["MysteryForCausalLM"]))
+    assert known_architectures() == ["Qwen2MoeForCausalLM"]
+
+
+def test_registry_takes_another_architecture(tiny_a):
+    calls = []
+
+    def parse(obj, where):
+        calls.append(where)
+        return Qwen2MoeConfig.from_json(dict(obj, architectures=["Qwen2MoeForCausalLM"]), where)
+
+    from inferx_b200.models.qwen2_moe import build_spec
+    register_architecture("ToyForCausalLM", parse, build_spec)
+    try:
+        cfg, spec = config_from_json(dict(tiny_a, architectures=["ToyForCausalLM"]))
+        assert calls and len(spec.layers) == 2
+        with pytest.raises(KeyError):
+            register_architecture("ToyForCausalLM", parse, build_spec)
+    finally:
+        reg._ARCHITECTURES.pop("ToyForCausalLM", None)
+
+
+def test_attention_bias_spellings_and_eos(tiny_a):
+    assert config_from_json(dict(tiny_a, attention_bias=False))[0].attention_bias is False
+    assert config_from_json(dict(tiny_a, qkv_bias=False))[0].attention_bias is False
+    assert config_from_json(dict(tiny_a, eos_token_id=7))[0].eos_token_ids == (7,)
+    with pytest.raises(ConfigError):
+        config_from_json(dict(tiny_a, eos_token_id="7"))
+
+
+def test_from_dir_and_duplicate_keys(tmp_path, tiny_b):
+    (tmp_path / "config.json").write_text(json.dumps(tiny_b))
+    cfg, _ = config_from_dir(str(tmp_path))
+    assert cfg.to_json()["sliding_window"] == 8
+    # the round trip parses to the same config
+    assert Qwen2MoeConfig.from_json(cfg.to_json()) == cfg
+    (tmp_path / "config.json").write_text('{"hidden_size": 1, "hidden_size": 2}')
+    with pytest.raises(ConfigError, match="duplicate key"):
+        config_from_dir(str(tmp_path))
+    with pytest.raises(ConfigError, match="no config.json"):
+        config_from_dir(str(tmp_path / "missing"))
