@@ -37,10 +37,11 @@ def pages_for(max_tokens: int, page_size: int) -> int:
 
 class ReplaySession:
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, *, page_size: int = 16,
-                 max_live: int = 8, device: str = "cuda", ops=None):
+                 max_live: int = 8, device: str = "cuda", ops=None, use_graphs: bool = False):
         _, model = load_model(model_dir, dtype=dtype, device=device, ops=ops)
         self.runtime = Runtime(model, page_size=page_size,
-                               num_pages=pages_for(max_tokens, page_size), max_slots=max_live)
+                               num_pages=pages_for(max_tokens, page_size), max_slots=max_live,
+                               use_graphs=use_graphs)
         self.manager = self.runtime.manager
         self.executor = self.runtime.executor
 

@@ -84,9 +84,10 @@ class LayerSpec:
 
 @dataclass(frozen=True)
 class RunEntry:
-    """One execution of a layer.  ``cache_of`` names the layer whose cache this
-    run reads and writes (its own by default); naming another layer makes this
-    run read that layer's keys and values without writing any."""
+    """One execution of a layer.  By default the run keeps its own cache (it writes
+    this step's keys and values, then reads).  ``cache_of`` names a layer whose
+    cache this run only reads: another layer's, or its own when the layer is run a
+    second time in the schedule and must see what its first run stored."""
     layer: int
     cache_of: Optional[int] = None
 
@@ -96,7 +97,7 @@ class RunEntry:
 
     @property
     def writes_cache(self) -> bool:
-        return self.cache_of is None or self.cache_of == self.layer
+        return self.cache_of is None
 
 
 @dataclass(frozen=True)
