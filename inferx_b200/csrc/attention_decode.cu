@@ -57,13 +57,14 @@ template <bool FAST> __device__ __forceinline__ float ix_exp2(float x) {
   return exp2f(x);
 }
 
-template <typename TA, int HD, int G, bool FAST>
+template <typename TA, int HD, int G, bool FAST, bool POW2>
 __global__ void __launch_bounds__(DEC_THREADS)
 attn_decode_split_kernel(const TA* __restrict__ q, const TA* __restrict__ kc,
                          const TA* __restrict__ vc, const int* __restrict__ block_table,
                          const int* __restrict__ kv_len, float* __restrict__ part_o,
                          float* __restrict__ part_ml, TA* __restrict__ out, int heads, int kvh,
-                         int page_size, int maxb, int window, float scale_log2e, int splits) {
+                         int page_size, int page_shift, int maxb, int window, float scale_log2e,
+                         int splits) {
   constexpr int EPL = Vec16<TA>::N;   // elements per 16-byte load
   constexpr int LPK = HD / EPL;       // lanes that share one key
   constexpr int KPI = 32 / LPK;       // keys per warp per load
@@ -118,9 +119,11 @@ attn_decode_split_kernel(const TA* __restrict__ q, const TA* __restrict__ kc,
       kraw[u] = make_uint4(0, 0, 0, 0);
       vraw[u] = make_uint4(0, 0, 0, 0);
       if (valid[u]) {
-        const int page = bt[kidx / page_size];
-        const size_t off =
-            (((size_t)page * kvh + kh) * page_size + kidx % page_size) * HD + c * EPL;
+        // a runtime integer division costs more than the dot product it feeds
+        const int pi = POW2 ? (kidx >> page_shift) : (kidx / page_size);
+        const int po = POW2 ? (kidx & (page_size - 1)) : (kidx % page_size);
+        const int page = bt[pi];
+        const size_t off = (((size_t)page * kvh + kh) * page_size + po) * HD + c * EPL;
         kraw[u] = *reinterpret_cast<const uint4*>(kc + off);
         vraw[u] = *reinterpret_cast<const uint4*>(vc + off);
       }
@@ -251,11 +254,21 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const in
   const int rep = heads / kvh;
   const float sl2 = scale * 1.4426950408889634f;
   const int G = rep % 8 == 0 ? 8 : (rep % 4 == 0 ? 4 : (rep % 2 == 0 ? 2 : 1));
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
   dim3 grid(splits, kvh * (rep / G), S);
-#define IX_DEC(GG)                                                                            \
-  attn_decode_split_kernel<TA, HD, GG, FAST><<<grid, DEC_THREADS, 0, stream>>>(                \
-      (const TA*)q, (const TA*)kc, (const TA*)vc, bt, kv_len, part_o, part_ml, (TA*)out, heads, \
-      kvh, page_size, maxb, window, sl2, splits)
+#define IX_DEC(GG)                                                                              \
+  do {                                                                                          \
+    if (page_shift >= 0)                                                                        \
+      attn_decode_split_kernel<TA, HD, GG, FAST, true><<<grid, DEC_THREADS, 0, stream>>>(        \
+          (const TA*)q, (const TA*)kc, (const TA*)vc, bt, kv_len, part_o, part_ml, (TA*)out,    \
+          heads, kvh, page_size, page_shift, maxb, window, sl2, splits);                        \
+    else                                                                                        \
+      attn_decode_split_kernel<TA, HD, GG, FAST, false><<<grid, DEC_THREADS, 0, stream>>>(       \
+          (const TA*)q, (const TA*)kc, (const TA*)vc, bt, kv_len, part_o, part_ml, (TA*)out,    \
+          heads, kvh, page_size, page_shift, maxb, window, sl2, splits);                        \
+  } while (0)
   if (G == 8) IX_DEC(8);
   else if (G == 4) IX_DEC(4);
   else if (G == 2) IX_DEC(2);

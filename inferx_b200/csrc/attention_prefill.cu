@@ -74,8 +74,8 @@ __global__ void __launch_bounds__(PF_THREADS)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
                     const bf16* __restrict__ vc, const int* __restrict__ block_table,
                     const int* __restrict__ cu_q, const int* __restrict__ q_pos0,
-                    bf16* __restrict__ out, int S, int heads, int kvh, int page_size, int maxb,
-                    int window, float scale_log2e) {
+                    bf16* __restrict__ out, int S, int heads, int kvh, int page_size,
+                    int page_shift, int maxb, int window, float scale_log2e) {
   constexpr int CH = HD / 8;            // 16-byte chunks per row
   constexpr int KS = HD / 16;           // k-steps of Q K^T
   constexpr int DT = HD / 8;            // n-tiles of the output
@@ -129,8 +129,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
       const bool ok = kp >= kv_lo && kp < kv_hi;
       size_t off = 0;
       if (ok) {
-        const int page = bt[kp / page_size];
-        off = (((size_t)page * kvh + kh) * page_size + kp % page_size) * HD + c * 8;
+        const int pi = page_shift >= 0 ? (kp >> page_shift) : (kp / page_size);
+        const int po = page_shift >= 0 ? (kp & (page_size - 1)) : (kp % page_size);
+        off = (((size_t)bt[pi] * kvh + kh) * page_size + po) * HD + c * 8;
       }
       cp_async16(kd + swz<CH>(r, c), kc + off, ok);
       cp_async16(vd + swz<CH>(r, c), vc + off, ok);
@@ -285,9 +286,13 @@ static int launch_prefill(const void* q, const void* kc, const void* vc, const i
   const int tiles = (T + PF_BM - 1) / PF_BM + S;   // every sequence can add one partial tile
   if (heads > 65535) return IX_ERR_SIZE;
   dim3 grid(tiles, heads);
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
   kern<<<grid, PF_THREADS, smem, stream>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, bt,
                                            cu_q, q_pos0, (bf16*)out, S, heads, kvh, page_size,
-                                           maxb, window, scale * 1.4426950408889634f);
+                                           page_shift, maxb, window,
+                                           scale * 1.4426950408889634f);
   return ix_launch_status();
 }
 

@@ -7,6 +7,7 @@
 // AddSharedExpertKernel (src/backends/cuda/ops/moe.cu:237-255,275-287).
 // The residual stream is kept in 32-bit here, so the residual sum never rounds.
 #include "common.cuh"
+#include "elementwise_vec.cuh"
 
 // ---------------------------------------------------------------------------
 // embedding: out[t, :] = table[ids[t], :] widened to fp32 (the residual stream)
@@ -22,11 +23,31 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
   for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
 }
 
+__global__ void embed_bf16_vec_kernel(const uint4* __restrict__ table, const int* __restrict__ ids,
+                                      float4* __restrict__ out, int chunks, int V) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= V) id = 0;
+  const uint4* row = table + (size_t)id * chunks;
+  float4* o = out + (size_t)t * chunks * 2;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    float f[8];
+    bf8_to_f32(row[c], f);
+    o[2 * c] = make_float4(f[0], f[1], f[2], f[3]);
+    o[2 * c + 1] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+}
+
 IX_API int ix_embed(const void* table, int table_dtype, const int* ids, int T, int H, int V,
                     float* out, cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (H <= 0 || V <= 0) return IX_ERR_SIZE;
   const int threads = H >= 1024 ? 256 : 128;
+  if (table_dtype == IX_BF16 && H % 8 == 0 && (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
+    embed_bf16_vec_kernel<<<T, threads, 0, stream>>>((const uint4*)table, ids, (float4*)out, H / 8,
+                                                     V);
+    return ix_launch_status();
+  }
   IX_DISPATCH_DTYPE(table_dtype, TW,
                     (embed_kernel<TW><<<T, threads, 0, stream>>>((const TW*)table, ids, out, H, V)));
   return ix_launch_status();
@@ -66,12 +87,86 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restri
   }
 }
 
+// bf16 activations, H a multiple of 8: each thread keeps up to NI chunks of 8 values in
+// registers, so the row is read once.  Same sum order as the scalar kernel is not
+// needed for equality between batches (a row is always reduced by one block the same way).
+template <int NI>
+__global__ void add_rmsnorm_bf16_vec_kernel(float* __restrict__ resid, const bf16* __restrict__ delta,
+                                            const float* __restrict__ gain,
+                                            const int* __restrict__ rows, bf16* __restrict__ out,
+                                            int H, float eps, int write_resid) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  float4* x = reinterpret_cast<float4*>(resid + src * H);
+  const uint4* d = delta ? reinterpret_cast<const uint4*>(delta + src * H) : nullptr;
+  const int chunks = H >> 3;
+  float v[NI][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < chunks) {
+      const float4 a = x[2 * c], b = x[2 * c + 1];
+      v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
+      v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
+      if (d) {
+        float f[8];
+        bf8_to_f32(d[c], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] += f[j];
+      }
+      if (write_resid && d) {
+        x[2 * c] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+        x[2 * c + 1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)H + eps);
+  uint4* o = reinterpret_cast<uint4*>(out + (size_t)r * H);
+  const float4* gw = reinterpret_cast<const float4*>(gain);
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < chunks) {
+      const float4 ga = gw[2 * c], gb = gw[2 * c + 1];
+      float f[8];
+      f[0] = v[i][0] * inv * ga.x; f[1] = v[i][1] * inv * ga.y;
+      f[2] = v[i][2] * inv * ga.z; f[3] = v[i][3] * inv * ga.w;
+      f[4] = v[i][4] * inv * gb.x; f[5] = v[i][5] * inv * gb.y;
+      f[6] = v[i][6] * inv * gb.z; f[7] = v[i][7] * inv * gb.w;
+      o[c] = f32_to_bf8(f);
+    }
+  }
+}
+
 IX_API int ix_add_rmsnorm(float* resid, const void* delta, const float* gain, const int* rows,
                           void* out, int act_dtype, int R, int H, float eps, int write_resid,
                           cudaStream_t stream) {
   if (R <= 0) return IX_OK;
   if (H <= 0) return IX_ERR_SIZE;
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  if (act_dtype == IX_BF16 && H % 8 == 0 &&
+      (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)gain | (uintptr_t)out) & 15) == 0) {
+    const int chunks = H / 8;
+    const int vt = chunks >= 256 ? 256 : (chunks >= 128 ? 128 : 64);
+    const int ni = (chunks + vt - 1) / vt;
+    if (ni <= 4) {
+      if (ni == 1)
+        add_rmsnorm_bf16_vec_kernel<1><<<R, vt, 0, stream>>>(resid, (const bf16*)delta, gain, rows,
+                                                             (bf16*)out, H, eps, write_resid);
+      else if (ni == 2)
+        add_rmsnorm_bf16_vec_kernel<2><<<R, vt, 0, stream>>>(resid, (const bf16*)delta, gain, rows,
+                                                             (bf16*)out, H, eps, write_resid);
+      else
+        add_rmsnorm_bf16_vec_kernel<4><<<R, vt, 0, stream>>>(resid, (const bf16*)delta, gain, rows,
+                                                             (bf16*)out, H, eps, write_resid);
+      return ix_launch_status();
+    }
+  }
   IX_DISPATCH_DTYPE(act_dtype, TA,
                     (add_rmsnorm_kernel<TA><<<R, threads, 0, stream>>>(
                         resid, (const TA*)delta, gain, rows, (TA*)out, H, eps, write_resid)));
@@ -94,11 +189,34 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
   }
 }
 
+__global__ void silu_mul_bf16_vec_kernel(const uint4* __restrict__ gu, uint4* __restrict__ out,
+                                         long long total_chunks, int chunks_per_row) {
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total_chunks;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / chunks_per_row;
+    const int c = (int)(idx - t * chunks_per_row);
+    float g[8], u[8], o[8];
+    bf8_to_f32(gu[t * 2 * chunks_per_row + c], g);
+    bf8_to_f32(gu[t * 2 * chunks_per_row + chunks_per_row + c], u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
+    out[idx] = f32_to_bf8(o);
+  }
+}
+
 IX_API int ix_silu_mul(const void* gu, void* out, int act_dtype, int T, int I,
                        cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (I <= 0) return IX_ERR_SIZE;
   const long long total = (long long)T * I;
+  if (act_dtype == IX_BF16 && I % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
+    const long long chunks = total / 8;
+    long long vb = (chunks + 255) / 256;
+    if (vb > 148 * 16) vb = 148 * 16;
+    silu_mul_bf16_vec_kernel<<<(int)vb, 256, 0, stream>>>((const uint4*)gu, (uint4*)out, chunks,
+                                                          I / 8);
+    return ix_launch_status();
+  }
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   IX_DISPATCH_DTYPE(act_dtype, TA,
@@ -131,12 +249,48 @@ __global__ void moe_combine_kernel(const TA* __restrict__ y, const int* __restri
   }
 }
 
+__global__ void moe_combine_bf16_vec_kernel(const uint4* __restrict__ y, const int* __restrict__ dest,
+                                            const float* __restrict__ w,
+                                            const uint4* __restrict__ shared,
+                                            const float* __restrict__ shared_logit,
+                                            uint4* __restrict__ out, int chunks, int k) {
+  const int t = blockIdx.x;
+  float sg = 1.0f;
+  if (shared && shared_logit) sg = 1.0f / (1.0f + expf(-shared_logit[t]));
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < k; ++s) {
+      const int row = dest[t * k + s];
+      const float ws = w[t * k + s];
+      float f[8];
+      bf8_to_f32(y[(size_t)row * chunks + c], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += ws * f[j];
+    }
+    if (shared) {
+      float f[8];
+      bf8_to_f32(shared[(size_t)t * chunks + c], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += sg * f[j];
+    }
+    out[(size_t)t * chunks + c] = f32_to_bf8(acc);
+  }
+}
+
 IX_API int ix_moe_combine(const void* y, const int* dest, const float* w, const void* shared,
                           const float* shared_logit, void* out, int act_dtype, int T, int H, int k,
                           cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (H <= 0 || k <= 0) return IX_ERR_SIZE;
   const int threads = H >= 1024 ? 256 : 128;
+  if (act_dtype == IX_BF16 && H % 8 == 0 &&
+      (((uintptr_t)y | (uintptr_t)shared | (uintptr_t)out) & 15) == 0) {
+    moe_combine_bf16_vec_kernel<<<T, H >= 2048 ? 256 : 128, 0, stream>>>(
+        (const uint4*)y, dest, w, (const uint4*)shared, shared_logit, (uint4*)out, H / 8, k);
+    return ix_launch_status();
+  }
   IX_DISPATCH_DTYPE(act_dtype, TA,
                     (moe_combine_kernel<TA><<<T, threads, 0, stream>>>(
                         (const TA*)y, dest, w, (const TA*)shared, shared_logit, (TA*)out, H, k)));

@@ -47,12 +47,17 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, unsigned a0, unsigned a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <typename TO, bool DUAL, int NT>
-__global__ void __launch_bounds__(SM_THREADS)
+template <typename TO, bool DUAL, int NT, int KSPLIT>
+__global__ void __launch_bounds__(SM_THREADS, (KSPLIT == 1 || NT >= 4) ? 1 : 2)
 gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
                     const int* __restrict__ offsets, const bf16* __restrict__ w,
                     TO* __restrict__ out, int M_single, int N, int K, long long w_expert_stride) {
-  __shared__ float red[DUAL ? 2 : 1][SM_WARPS][NT][4][32];
+  constexpr int TILES = SM_WARPS / KSPLIT;        // 16-column tiles per block
+  // k-steps kept in flight per warp: deep when a warp streams all of K for its tile,
+  // shallower when K is split over warps (more warps resident instead)
+  constexpr int D = KSPLIT == 1 ? (DUAL ? 4 : (NT >= 4 ? 4 : 8)) : (DUAL ? 2 : (NT >= 4 ? 2 : 4));
+  __shared__ float red[KSPLIT > 1 ? (DUAL ? 2 : 1) : 1][KSPLIT > 1 ? SM_WARPS : 1]
+                      [KSPLIT > 1 ? NT : 1][4][32];
   const int e = blockIdx.y;
   int lo, hi;
   if (offsets) {
@@ -65,7 +70,8 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
   if (lo >= hi) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int j0 = blockIdx.x * 16;
+  const int tile = warp / KSPLIT, ks = warp % KSPLIT;
+  const int j0 = (blockIdx.x * TILES + tile) * 16;
   const int ja = j0 + g, jb = j0 + g + 8;
   const bool ja_ok = ja < N, jb_ok = jb < N;
   const bf16* wbase = w + (size_t)e * w_expert_stride;
@@ -74,6 +80,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
   const bf16* ua = wa + (size_t)N * K;   // up rows follow the gate rows (DUAL)
   const bf16* ub = wb + (size_t)N * K;
   const int ksteps = (K + 31) >> 5;
+  const int my_steps = ksteps > ks ? (ksteps - ks + KSPLIT - 1) / KSPLIT : 0;
   const uint4 zero = make_uint4(0, 0, 0, 0);
 
   for (int r0 = lo; r0 < hi; r0 += 8 * NT) {
@@ -94,93 +101,132 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
         acc[i][c] = 0.f;
         if (DUAL) acc2[i][c] = 0.f;
       }
-    constexpr int UNR = DUAL ? 4 : 8;
-    for (int s0 = warp; s0 < ksteps; s0 += SM_WARPS * UNR) {
-      uint4 va[UNR], vb[UNR], vua[DUAL ? UNR : 1], vub[DUAL ? UNR : 1];
-#pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const int kb = (s0 + u * SM_WARPS) * 32 + t * 8;
-        const bool kok = kb < K;
-        va[u] = (kok && ja_ok) ? ld_stream16(wa + kb) : zero;
-        vb[u] = (kok && jb_ok) ? ld_stream16(wb + kb) : zero;
-        if (DUAL) {
-          vua[u] = (kok && ja_ok) ? ld_stream16(ua + kb) : zero;
-          vub[u] = (kok && jb_ok) ? ld_stream16(ub + kb) : zero;
-        }
+    // a ring of D k-steps in registers: weights and the matching activations
+    uint4 va[D], vb[D], vua[DUAL ? D : 1], vub[DUAL ? D : 1], vx[D][NT];
+    auto fetch = [&](int u, int idx) {
+      const int kb = (ks + idx * KSPLIT) * 32 + t * 8;
+      const bool kok = idx < my_steps && kb < K;
+      va[u] = (kok && ja_ok) ? ld_stream16(wa + kb) : zero;
+      vb[u] = (kok && jb_ok) ? ld_stream16(wb + kb) : zero;
+      if (DUAL) {
+        vua[u] = (kok && ja_ok) ? ld_stream16(ua + kb) : zero;
+        vub[u] = (kok && jb_ok) ? ld_stream16(ub + kb) : zero;
       }
 #pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const int kb = (s0 + u * SM_WARPS) * 32 + t * 8;
-        const bool kok = kb < K;
+      for (int i = 0; i < NT; ++i)
+        vx[u][i] = (kok && xok[i]) ? *reinterpret_cast<const uint4*>(xrow[i] + kb) : zero;
+    };
+#pragma unroll
+    for (int u = 0; u < D; ++u) fetch(u, u);
+    for (int base = 0; base < my_steps; base += D) {
+#pragma unroll
+      for (int u = 0; u < D; ++u) {
 #pragma unroll
         for (int i = 0; i < NT; ++i) {
-          uint4 xv = zero;
-          if (kok && xok[i]) xv = *reinterpret_cast<const uint4*>(xrow[i] + kb);
-          mma_bf16_16816(acc[i], va[u].x, vb[u].x, va[u].y, vb[u].y, xv.x, xv.y);
-          mma_bf16_16816(acc[i], va[u].z, vb[u].z, va[u].w, vb[u].w, xv.z, xv.w);
+          mma_bf16_16816(acc[i], va[u].x, vb[u].x, va[u].y, vb[u].y, vx[u][i].x, vx[u][i].y);
+          mma_bf16_16816(acc[i], va[u].z, vb[u].z, va[u].w, vb[u].w, vx[u][i].z, vx[u][i].w);
           if (DUAL) {
-            mma_bf16_16816(acc2[i], vua[u].x, vub[u].x, vua[u].y, vub[u].y, xv.x, xv.y);
-            mma_bf16_16816(acc2[i], vua[u].z, vub[u].z, vua[u].w, vub[u].w, xv.z, xv.w);
+            mma_bf16_16816(acc2[i], vua[u].x, vub[u].x, vua[u].y, vub[u].y, vx[u][i].x,
+                           vx[u][i].y);
+            mma_bf16_16816(acc2[i], vua[u].z, vub[u].z, vua[u].w, vub[u].w, vx[u][i].z,
+                           vx[u][i].w);
           }
         }
+        fetch(u, base + u + D);   // zeros beyond the last step
       }
     }
-    __syncthreads();   // the previous pass has read its sums
+    if (KSPLIT == 1) {
+      // this warp holds complete sums: c0,c1 -> (column g, rows 2t, 2t+1); c2,c3 -> column g+8
 #pragma unroll
-    for (int i = 0; i < NT; ++i)
+      for (int i = 0; i < NT; ++i)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        red[0][warp][i][c][lane] = acc[i][c];
-        if (DUAL) red[1][warp][i][c][lane] = acc2[i][c];
-      }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < NT * 128; idx += SM_THREADS) {
-      const int l = idx & 31, c = (idx >> 5) & 3, i = idx >> 7;
-      float v = 0.f, v2 = 0.f;
+        for (int c = 0; c < 4; ++c) {
+          const int j = (c & 2) ? jb : ja;
+          const int r = r0 + i * 8 + 2 * t + (c & 1);
+          if (j < N && r < hi) {
+            float v = acc[i][c];
+            if (DUAL) v = v / (1.0f + __expf(-v)) * acc2[i][c];
+            out[(size_t)r * N + j] = from_f32<TO>(v);
+          }
+        }
+    } else {
+      __syncthreads();   // the previous pass has read its sums
 #pragma unroll
-      for (int wq = 0; wq < SM_WARPS; ++wq) {
-        v += red[0][wq][i][c][l];
-        if (DUAL) v2 += red[1][wq][i][c][l];
-      }
-      const int gg = l >> 2, tt = l & 3;
-      const int j = j0 + ((c & 2) ? gg + 8 : gg);
-      const int r = r0 + i * 8 + 2 * tt + (c & 1);
-      if (j < N && r < hi) {
-        if (DUAL) v = v / (1.0f + __expf(-v)) * v2;
-        out[(size_t)r * N + j] = from_f32<TO>(v);
+      for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          red[0][warp][i][c][lane] = acc[i][c];
+          if (DUAL) red[DUAL ? 1 : 0][warp][i][c][lane] = acc2[i][c];
+        }
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < TILES * NT * 128; idx += SM_THREADS) {
+        const int l = idx & 31, c = (idx >> 5) & 3, i = (idx >> 7) % NT, ti = idx / (NT * 128);
+        float v = 0.f, v2 = 0.f;
+#pragma unroll
+        for (int q = 0; q < KSPLIT; ++q) {
+          v += red[0][ti * KSPLIT + q][i][c][l];
+          if (DUAL) v2 += red[DUAL ? 1 : 0][ti * KSPLIT + q][i][c][l];
+        }
+        const int gg = l >> 2, tt = l & 3;
+        const int j = (blockIdx.x * TILES + ti) * 16 + ((c & 2) ? gg + 8 : gg);
+        const int r = r0 + i * 8 + 2 * tt + (c & 1);
+        if (j < N && r < hi) {
+          if (DUAL) v = v / (1.0f + __expf(-v)) * v2;
+          out[(size_t)r * N + j] = from_f32<TO>(v);
+        }
       }
     }
   }
 }
 
-template <typename TO, bool DUAL, int NT>
-static int launch_small_m(const void* x, const int* rows, const int* offsets, const void* w,
-                          void* out, int M, int N, int K, int E, cudaStream_t stream) {
+template <typename TO, bool DUAL, int NT, int KSPLIT>
+static int launch_small_m2(const void* x, const int* rows, const int* offsets, const void* w,
+                           void* out, int M, int N, int K, int E, cudaStream_t stream) {
   if (E > 65535) return IX_ERR_SIZE;
   const long long w_rows = DUAL ? 2LL * N : N;
-  dim3 grid((N + 15) / 16, E);
-  gemm_small_m_kernel<TO, DUAL, NT><<<grid, SM_THREADS, 0, stream>>>(
+  constexpr int TILES = SM_WARPS / KSPLIT;
+  dim3 grid((N + 16 * TILES - 1) / (16 * TILES), E);
+  gemm_small_m_kernel<TO, DUAL, NT, KSPLIT><<<grid, SM_THREADS, 0, stream>>>(
       (const bf16*)x, rows, offsets, (const bf16*)w, (TO*)out, offsets ? 0 : M, N, K, w_rows * K);
   return ix_launch_status();
 }
 
+template <typename TO, bool DUAL, int NT>
+static int launch_small_m(const void* x, const int* rows, const int* offsets, const void* w,
+                          void* out, int M, int N, int K, int E, int active_groups,
+                          cudaStream_t stream) {
+  // enough warps to keep every SM streaming: split K over warps when there are few tiles
+  const long long tiles = (long long)((N + 15) / 16) * (active_groups > 0 ? active_groups : 1);
+  int ksplit = 1;
+  while (ksplit < 8 && tiles * ksplit < 148 * 8) ksplit *= 2;
+  if (ksplit == 1)
+    return launch_small_m2<TO, DUAL, NT, 1>(x, rows, offsets, w, out, M, N, K, E, stream);
+  if (ksplit == 2)
+    return launch_small_m2<TO, DUAL, NT, 2>(x, rows, offsets, w, out, M, N, K, E, stream);
+  if (ksplit == 4)
+    return launch_small_m2<TO, DUAL, NT, 4>(x, rows, offsets, w, out, M, N, K, E, stream);
+  return launch_small_m2<TO, DUAL, NT, 8>(x, rows, offsets, w, out, M, N, K, E, stream);
+}
+
 // x: [*, K] bf16; w: [E, N (or 2N when dual), K] bf16; out: [rows, N] bf16 or fp32.
 // offsets == null: one matrix (E must be 1) with M rows.  rows_per_pass: 8, 16 or 32
-// activation rows handled per pass over a group's weights.
+// activation rows handled per pass over a group's weights.  active_groups: how many
+// groups are expected to have rows (a hint for how to spread the work; 0 = all).
 IX_API int ix_gemm_small_m(const void* x, const int* rows, const int* offsets, const void* w,
                            void* out, int out_dtype, int dual, int M, int N, int K, int E,
-                           int rows_per_pass, cudaStream_t stream) {
+                           int rows_per_pass, int active_groups, cudaStream_t stream) {
   if (N <= 0 || K <= 0 || E <= 0) return IX_ERR_SIZE;
   if (K % 8 != 0) return IX_ERR_UNSUPPORTED;
   if (!offsets && E != 1) return IX_ERR_SIZE;
   if (!offsets && M <= 0) return IX_OK;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return IX_ERR_ALIGN;
   const int nt = rows_per_pass > 16 ? 4 : (rows_per_pass > 8 ? 2 : 1);
+  if (active_groups <= 0 || active_groups > E) active_groups = E;
 #define IX_SM(TO, D)                                                                          \
   do {                                                                                        \
-    if (nt == 4) return launch_small_m<TO, D, 4>(x, rows, offsets, w, out, M, N, K, E, stream); \
-    if (nt == 2) return launch_small_m<TO, D, 2>(x, rows, offsets, w, out, M, N, K, E, stream); \
-    return launch_small_m<TO, D, 1>(x, rows, offsets, w, out, M, N, K, E, stream);             \
+    if (nt == 4) return launch_small_m<TO, D, 4>(x, rows, offsets, w, out, M, N, K, E, active_groups, stream); \
+    if (nt == 2) return launch_small_m<TO, D, 2>(x, rows, offsets, w, out, M, N, K, E, active_groups, stream); \
+    return launch_small_m<TO, D, 1>(x, rows, offsets, w, out, M, N, K, E, active_groups, stream); \
   } while (0)
   if (out_dtype == IX_BF16) {
     if (dual) IX_SM(bf16, true);

@@ -256,11 +256,95 @@ moe_dispatch_kernel(const int* __restrict__ topk_idx, int A, int E, int k,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Dispatch for many assignments: blocks of 1024 assignments count their experts,
+// one block turns the counts into bases (per block and expert) and offsets, and the
+// blocks place their assignments: position = offsets[e] + (rows of e in earlier
+// blocks) + (rows of e in earlier warps of this block) + (rank inside the warp).
+// Stable, and free of atomics on global memory.  scratch: [blocks + 1][E] ints.
+// ---------------------------------------------------------------------------
+#define DISPATCH_CHUNK 1024
+#define DISPATCH_MAX_E 512
+
+__global__ void __launch_bounds__(DISPATCH_CHUNK)
+dispatch_count_kernel(const int* __restrict__ topk_idx, int A, int E, int* __restrict__ counts) {
+  __shared__ int hist[DISPATCH_MAX_E];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int a = blockIdx.x * DISPATCH_CHUNK + threadIdx.x;
+  if (a < A) atomicAdd(&hist[topk_idx[a]], 1);   // counts do not depend on the order
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[(size_t)blockIdx.x * E + e] = hist[e];
+}
+
+__global__ void __launch_bounds__(DISPATCH_MAX_E)
+dispatch_scan_kernel(int* __restrict__ counts, int blocks, int E, int* __restrict__ offsets) {
+  __shared__ int total[DISPATCH_MAX_E];
+  const int e = threadIdx.x;
+  if (e < E) {
+    int run = 0;
+    for (int b = 0; b < blocks; ++b) {
+      const int c = counts[(size_t)b * E + e];
+      counts[(size_t)b * E + e] = run;   // rows of e in earlier blocks
+      run += c;
+    }
+    total[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int i = 0; i < E; ++i) {
+      offsets[i] = run;
+      run += total[i];
+    }
+    offsets[E] = run;
+  }
+}
+
+__global__ void __launch_bounds__(DISPATCH_CHUNK)
+dispatch_place_kernel(const int* __restrict__ topk_idx, int A, int E, int k,
+                      const int* __restrict__ bases, const int* __restrict__ offsets,
+                      int* __restrict__ rows, int* __restrict__ dest) {
+  extern __shared__ int warp_count[];   // [32][E]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) warp_count[i] = 0;
+  __syncthreads();
+  const int a = blockIdx.x * DISPATCH_CHUNK + threadIdx.x;
+  const int e = a < A ? topk_idx[a] : -1 - lane;   // idle lanes match nobody
+  const unsigned same = __match_any_sync(0xffffffffu, e);
+  const int rank = __popc(same & ((1u << lane) - 1u));
+  if (a < A && rank == 0) warp_count[warp * E + e] = __popc(same);
+  __syncthreads();
+  if (a < A) {
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_count[w * E + e];
+    const int r = offsets[e] + bases[(size_t)blockIdx.x * E + e] + before + rank;
+    rows[r] = a / k;
+    dest[a] = r;
+  }
+}
+
+// scratch: ints for ix_moe_dispatch_scratch_ints(T, E, k) entries, or null to force the
+// single-block kernel.
+IX_API int ix_moe_dispatch_scratch_ints(int T, int E, int k) {
+  const long long A = (long long)T * k;
+  if (A <= 2048 || E > DISPATCH_MAX_E) return 0;
+  return (int)(((A + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK) * E);
+}
+
 IX_API int ix_moe_dispatch(const int* topk_idx, int T, int E, int k, int* offsets, int* rows,
-                           int* dest, cudaStream_t stream) {
+                           int* dest, int* scratch, cudaStream_t stream) {
   if (E <= 0 || k <= 0 || E > 8192) return IX_ERR_SIZE;
   if (T < 0) return IX_ERR_SIZE;
   const int A = T * k;
+  if (scratch && A > 2048 && E <= DISPATCH_MAX_E) {
+    const int blocks = (A + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK;
+    dispatch_count_kernel<<<blocks, DISPATCH_CHUNK, 0, stream>>>(topk_idx, A, E, scratch);
+    dispatch_scan_kernel<<<1, DISPATCH_MAX_E, 0, stream>>>(scratch, blocks, E, offsets);
+    dispatch_place_kernel<<<blocks, DISPATCH_CHUNK, 32 * E * sizeof(int), stream>>>(
+        topk_idx, A, E, k, scratch, offsets, rows, dest);
+    return ix_launch_status();
+  }
   const int threads = E >= 32 ? 1024 : 32 * E;
   moe_dispatch_kernel<<<1, threads, (E + 1) * sizeof(int), stream>>>(topk_idx, A, E, k, offsets,
                                                                     rows, dest);

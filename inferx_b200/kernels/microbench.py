@@ -26,12 +26,23 @@ import torch
 L2_BYTES = 126 << 20
 
 
+EAGER = [False]   # --eager: no graph capture (for profilers that want plain launches)
+
+
 def _time(fn, n_variants, iters, warmup=5):
     """Microseconds per call.  The calls are captured into one CUDA graph and the
     graph is replayed, so the host's launch cost does not hide a short kernel."""
     for i in range(warmup):
         fn(i % n_variants)
     torch.cuda.synchronize()
+    if EAGER[0]:
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for i in range(iters):
+            fn(i % n_variants)
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) * 1e3 / iters
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         for i in range(iters):
@@ -176,10 +187,12 @@ def main(argv=None):
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="plain launches, no graph capture")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench needs a CUDA device", file=sys.stderr)
         return 3
+    EAGER[0] = args.eager
     print(json.dumps(globals()[args.case](args)))
     return 0
 

@@ -291,9 +291,11 @@ def moe_dispatch(topk_idx: torch.Tensor, num_experts: int):
     offsets = torch.empty((num_experts + 1,), dtype=torch.int32, device=dev)
     rows = torch.empty((T * k,), dtype=torch.int32, device=dev)
     dest = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    n_scratch = _lib().ix_moe_dispatch_scratch_ints(T, num_experts, k)
+    scratch = torch.empty((n_scratch,), dtype=torch.int32, device=dev) if n_scratch else None
     _check(_lib().ix_moe_dispatch(_ptr(topk_idx), T, num_experts, k, _ptr(offsets), _ptr(rows),
-                                  _ptr(dest), _stream()), "moe_dispatch")
-    _count()
+                                  _ptr(dest), _ptr(scratch), _stream()), "moe_dispatch")
+    _count(3 if n_scratch else 1)
     return offsets, rows, dest
 
 
@@ -451,7 +453,8 @@ SMALL_M_DENSE_ROWS = 32      # dense: up to this many rows stream the weights on
 
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor],
                  offsets: Optional[torch.Tensor], dual: bool, num_out_rows: int,
-                 out_dtype: Optional[torch.dtype] = None, rows_per_pass: int = 8):
+                 out_dtype: Optional[torch.dtype] = None, rows_per_pass: int = 8,
+                 active_groups: int = 0):
     """Weight-streaming product for few rows per weight matrix (bf16 inputs)."""
     _chk("x", x, torch.bfloat16)
     _chk("w", w, torch.bfloat16)
@@ -466,7 +469,8 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor],
     code = _lib().ix_gemm_small_m(
         _ptr(x), _ptr(rows), _ptr(offsets), _ptr(w), _ptr(out),
         F32 if out_dtype == torch.float32 else BF16, 1 if dual else 0,
-        0 if offsets is not None else x.shape[0], N, K, E, rows_per_pass, _stream())
+        0 if offsets is not None else x.shape[0], N, K, E, rows_per_pass,
+        active_groups or min(E, num_out_rows), _stream())
     _check(code, "gemm_small_m")
     _count()
     return out

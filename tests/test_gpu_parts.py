@@ -46,6 +46,19 @@ def _tol(dtype):
     return dict(rtol=3e-2, atol=3e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)
 
 
+def _assert_close_scaled(out, ref, dtype):
+    """Error bound relative to the size of the reference: bfloat16 rounds every
+    intermediate to 8 bits of mantissa (2^-9 relative), a part has a handful of them."""
+    bound = (1.5e-2 if dtype == torch.bfloat16 else 2e-5) * float(ref.abs().max())
+    err = float((out - ref).abs().max())
+    assert err <= bound, f"max error {err:.3e} exceeds {bound:.3e}"
+
+
+@pytest.fixture(autouse=True)
+def _seed():
+    torch.manual_seed(1234)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_rmsnorm_part(dtype):
     ctx = _ctx(dtype)
@@ -69,8 +82,7 @@ def test_swiglu_part(dtype):
     for T in (3, 50):            # few rows (weight streaming) and many (library product)
         x = torch.randn(T, 72).to(dtype)
         out = part.forward(x.cuda())
-        torch.testing.assert_close(out.float().cpu(), plain.swiglu_mlp(w, "mlp", x.float()),
-                                   **_tol(dtype))
+        _assert_close_scaled(out.float().cpu(), plain.swiglu_mlp(w, "mlp", x.float()), dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -88,7 +100,7 @@ def test_moe_part(dtype, renorm, shared, gated):
         x = torch.randn(T, 64).to(dtype)
         out = part.forward(x.cuda())
         ref = plain.moe_block(cfg, w, "mlp", x.float())
-        torch.testing.assert_close(out.float().cpu(), ref, **_tol(dtype))
+        _assert_close_scaled(out.float().cpu(), ref, dtype)
 
 
 def _step_context(ctx, mixer, tokens_per_seq, page=4):
@@ -127,7 +139,7 @@ def test_attention_part(dtype, heads, kvh, hd, window, bias):
     at = 0
     for n in lens:
         ref = plain.attention_block(cfg, w, "attn", x[at:at + n].float(), torch.arange(n), window)
-        torch.testing.assert_close(out[at:at + n], ref, **_tol(dtype))
+        _assert_close_scaled(out[at:at + n], ref, dtype)
         at += n
 
 
