@@ -281,6 +281,284 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const in
   return ix_launch_status();
 }
 
+// ---------------------------------------------------------------------------
+// Tensor-core form of the split kernel (bf16, head_dim 64 or 128).  The scalar
+// kernel above spends several instructions per byte on unpacking and shuffles and
+// cannot keep up with HBM; here a block's four warps share 64-key tiles that
+// cp.async streams through a three-stage ring in shared memory, each warp takes 16
+// keys of the tile, computes S = Q K^T and O += P V with mma.sync.m16n8k16 (the up
+// to 16 query heads of the KV head are the M side) and keeps its own online
+// softmax; the warps' partials are merged through shared memory at the end.
+// Same scratch layout and merge kernel as the scalar form.
+// ---------------------------------------------------------------------------
+#define DM_BN 64
+#define DM_STAGES 3
+
+__device__ __forceinline__ void dm_cp16(void* smem, const void* gmem, bool valid) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void dm_ldsm(unsigned* r, const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+__device__ __forceinline__ void dm_ldsm_t(unsigned* r, const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+__device__ __forceinline__ void dm_mma(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <int CH> __device__ __forceinline__ int dm_swz(int r, int c) {
+  return (r * CH + (c ^ (r & 7))) * 16;
+}
+
+template <int HD, bool POW2>
+__global__ void __launch_bounds__(DEC_THREADS)
+attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
+                       const bf16* __restrict__ vc, const int* __restrict__ block_table,
+                       const int* __restrict__ kv_len, float* __restrict__ part_o,
+                       float* __restrict__ part_ml, bf16* __restrict__ out, int heads, int kvh,
+                       int page_size, int page_shift, int maxb, int window, float scale_log2e,
+                       int splits) {
+  constexpr int CH = HD / 8, KS = HD / 16, DT = HD / 8;
+  constexpr int TILE_BYTES = DM_BN * HD * 2;
+  extern __shared__ __align__(128) unsigned char dsm[];
+  unsigned char* Qs = dsm;                                   // [16][HD]
+  unsigned char* Ks = Qs + 16 * HD * 2;                      // [STAGES][64][HD]
+  unsigned char* Vs = Ks + DM_STAGES * TILE_BYTES;           // [STAGES][64][HD]
+  __shared__ float sm_m[DEC_WARPS][16];
+  __shared__ float sm_l[DEC_WARPS][16];
+
+  const int split = blockIdx.x, s = blockIdx.z;
+  const int rep = heads / kvh;
+  const int row_groups = (rep + 15) / 16;
+  const int kh = blockIdx.y / row_groups;
+  const int qrow0 = (blockIdx.y % row_groups) * 16;
+  const int rows_valid = min(16, rep - qrow0);
+  const int h0 = kh * rep + qrow0;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  const int len = kv_len[s];
+  const int start = window > 0 ? max(0, len - window) : 0;
+  const int n = len - start;
+  int chunk = (n + splits - 1) / splits;
+  chunk = (chunk + DM_BN - 1) / DM_BN * DM_BN;
+  const int k0 = start + split * chunk;
+  const int k1 = min(len, k0 + chunk);
+  const int n_tiles = k1 > k0 ? (k1 - k0 + DM_BN - 1) / DM_BN : 0;
+  const int* bt = block_table + (size_t)s * maxb;
+
+  for (int idx = tid; idx < 16 * CH; idx += DEC_THREADS) {
+    const int r = idx / CH, c = idx - r * CH;
+    const bool ok = r < rows_valid;
+    dm_cp16(Qs + dm_swz<CH>(r, c), q + ((size_t)s * heads + h0 + (ok ? r : 0)) * HD + c * 8, ok);
+  }
+  auto load_kv = [&](int it) {
+    if (it < n_tiles) {
+      const int stage = it % DM_STAGES;
+      const int kbase = k0 + it * DM_BN;
+      unsigned char* kd = Ks + stage * TILE_BYTES;
+      unsigned char* vd = Vs + stage * TILE_BYTES;
+      for (int idx = tid; idx < DM_BN * CH; idx += DEC_THREADS) {
+        const int r = idx / CH, c = idx - r * CH;
+        const int kp = kbase + r;
+        const bool ok = kp < k1;
+        size_t off = 0;
+        if (ok) {
+          const int pi = POW2 ? (kp >> page_shift) : (kp / page_size);
+          const int po = POW2 ? (kp & (page_size - 1)) : (kp % page_size);
+          off = (((size_t)bt[pi] * kvh + kh) * page_size + po) * HD + c * 8;
+        }
+        dm_cp16(kd + dm_swz<CH>(r, c), kc + off, ok);
+        dm_cp16(vd + dm_swz<CH>(r, c), vc + off, ok);
+      }
+    }
+    asm volatile("cp.async.commit_group;");
+  };
+  load_kv(0);
+  load_kv(1);
+
+  float o[DT][4];
+#pragma unroll
+  for (int j = 0; j < DT; ++j)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[j][c] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  unsigned qf[KS][4];
+
+  for (int it = 0; it < n_tiles; ++it) {
+    load_kv(it + 2);
+    asm volatile("cp.async.wait_group 2;");
+    __syncthreads();
+    if (it == 0) {
+#pragma unroll
+      for (int kk = 0; kk < KS; ++kk)
+        dm_ldsm(qf[kk], Qs + dm_swz<CH>((lane & 7) + ((lane >> 3) & 1) * 8, kk * 2 + (lane >> 4)));
+    }
+    const int stage = it % DM_STAGES;
+    const unsigned char* kt = Ks + stage * TILE_BYTES;
+    const unsigned char* vt = Vs + stage * TILE_BYTES;
+    const int kw = k0 + it * DM_BN + warp * 16;      // first key of this warp's 16
+    if (kw < k1) {
+      float sc[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sc[j][c] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < KS; ++kk) {
+        unsigned b[4];
+        dm_ldsm(b, kt + dm_swz<CH>(warp * 16 + (lane >> 4) * 8 + (lane & 7),
+                                   kk * 2 + ((lane >> 3) & 1)));
+        dm_mma(sc[0], qf[kk], b[0], b[1]);
+        dm_mma(sc[1], qf[kk], b[2], b[3]);
+      }
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int kp = kw + j * 8 + 2 * t + (c & 1);
+          const float v = kp < k1 ? sc[j][c] * scale_log2e : -INFINITY;
+          sc[j][c] = v;
+          mx[c >> 1] = fmaxf(mx[c >> 1], v);
+        }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_run[r], mx[r]);
+        m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+        corr[r] = ix_exp2<true>(m_run[r] - m_use[r]);
+        m_run[r] = m_new;
+        l_run[r] *= corr[r];
+      }
+#pragma unroll
+      for (int j = 0; j < DT; ++j) {
+        o[j][0] *= corr[0]; o[j][1] *= corr[0];
+        o[j][2] *= corr[1]; o[j][3] *= corr[1];
+      }
+      unsigned pf[4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float p0 = ix_exp2<true>(sc[j][0] - m_use[0]);
+        const float p1 = ix_exp2<true>(sc[j][1] - m_use[0]);
+        const float p2 = ix_exp2<true>(sc[j][2] - m_use[1]);
+        const float p3 = ix_exp2<true>(sc[j][3] - m_use[1]);
+        l_run[0] += p0 + p1;
+        l_run[1] += p2 + p3;
+        __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi = __floats2bfloat162_rn(p2, p3);
+        pf[j * 2 + 0] = *reinterpret_cast<unsigned*>(&lo);
+        pf[j * 2 + 1] = *reinterpret_cast<unsigned*>(&hi);
+      }
+#pragma unroll
+      for (int jd = 0; jd < DT; jd += 2) {
+        unsigned b[4];
+        dm_ldsm_t(b, vt + dm_swz<CH>(warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7),
+                                     jd + (lane >> 4)));
+        dm_mma(o[jd], pf, b[0], b[1]);
+        dm_mma(o[jd + 1], pf, b[2], b[3]);
+      }
+    }
+    __syncthreads();   // the stage may be refilled
+  }
+  asm volatile("cp.async.wait_group 0;");
+  __syncthreads();
+
+  // merge the four warps (each saw different keys); stage memory is free now
+  float* sm_o = reinterpret_cast<float*>(Ks);     // [DEC_WARPS][16][HD]
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  if (t == 0) {
+    sm_m[warp][g] = m_run[0];     sm_l[warp][g] = l_run[0];
+    sm_m[warp][g + 8] = m_run[1]; sm_l[warp][g + 8] = l_run[1];
+  }
+#pragma unroll
+  for (int j = 0; j < DT; ++j) {
+    const int d = j * 8 + 2 * t;
+    sm_o[(warp * 16 + g) * HD + d] = o[j][0];
+    sm_o[(warp * 16 + g) * HD + d + 1] = o[j][1];
+    sm_o[(warp * 16 + g + 8) * HD + d] = o[j][2];
+    sm_o[(warp * 16 + g + 8) * HD + d + 1] = o[j][3];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rows_valid * HD; idx += DEC_THREADS) {
+    const int r = idx / HD, d = idx - r * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm_m[w][r]);
+    float ov = 0.f, L = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; ++w) {
+        const float cw = ix_exp2<true>(sm_m[w][r] - M);   // exp2(-inf) = 0 for idle warps
+        ov += sm_o[(w * 16 + r) * HD + d] * cw;
+        L += sm_l[w][r] * cw;
+      }
+    }
+    const size_t hrow = (size_t)s * heads + h0 + r;
+    if (splits == 1) {
+      out[hrow * HD + d] = __float2bfloat16_rn(L > 0.f ? ov / L : 0.f);
+    } else {
+      part_o[(hrow * splits + split) * HD + d] = ov;
+      if (d == 0) {
+        part_ml[(hrow * splits + split) * 2] = M;
+        part_ml[(hrow * splits + split) * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+template <int HD>
+static int launch_decode_mma(const void* q, const void* kc, const void* vc, const int* bt,
+                             const int* kv_len, float* part_o, float* part_ml, void* out, int S,
+                             int heads, int kvh, int page_size, int maxb, int window, float scale,
+                             int splits, cudaStream_t stream) {
+  const int rep = heads / kvh;
+  const float sl2 = scale * 1.4426950408889634f;
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
+  const int smem = 16 * HD * 2 + 2 * DM_STAGES * DM_BN * HD * 2;
+  dim3 grid(splits, kvh * ((rep + 15) / 16), S);
+  cudaError_t e;
+  if (page_shift >= 0) {
+    auto kern = attn_decode_mma_kernel<HD, true>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<grid, DEC_THREADS, smem, stream>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, bt,
+                                              kv_len, part_o, part_ml, (bf16*)out, heads, kvh,
+                                              page_size, page_shift, maxb, window, sl2, splits);
+  } else {
+    auto kern = attn_decode_mma_kernel<HD, false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<grid, DEC_THREADS, smem, stream>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, bt,
+                                              kv_len, part_o, part_ml, (bf16*)out, heads, kvh,
+                                              page_size, page_shift, maxb, window, sl2, splits);
+  }
+  int rc = ix_launch_status();
+  if (rc != 0 || splits == 1) return rc;
+  attn_decode_merge_kernel<bf16, true><<<S * heads, HD >= 128 ? 128 : 64, 0, stream>>>(
+      part_o, part_ml, (bf16*)out, HD, splits);
+  return ix_launch_status();
+}
+
 // The number of splits a caller should provide scratch for.
 IX_API int ix_attn_decode_splits(int S, int heads, int kvh, int max_kv_len) {
   const int rep = heads / (kvh > 0 ? kvh : 1);
@@ -295,11 +573,13 @@ IX_API int ix_attn_decode_splits(int S, int heads, int kvh, int max_kv_len) {
   return (int)splits;
 }
 
-IX_API int ix_paged_attention_decode(const void* q, const void* k_cache, const void* v_cache,
-                                     const int* block_table, const int* kv_len, float* part_o,
-                                     float* part_ml, void* out, int act_dtype, int S, int heads,
-                                     int kvh, int hd, int page_size, int max_blocks, int window,
-                                     float scale, int splits, cudaStream_t stream) {
+// variant 0: the tensor-core kernel where it applies (bf16, head_dim 64/128), else the
+// scalar kernel; variant 1: always the scalar kernel.
+static int decode_dispatch(const void* q, const void* k_cache, const void* v_cache,
+                           const int* block_table, const int* kv_len, float* part_o,
+                           float* part_ml, void* out, int act_dtype, int S, int heads, int kvh,
+                           int hd, int page_size, int max_blocks, int window, float scale,
+                           int splits, int variant, cudaStream_t stream) {
   if (S <= 0) return IX_OK;
   if (heads <= 0 || kvh <= 0 || heads % kvh != 0 || page_size <= 0 || max_blocks <= 0 ||
       window < 0 || splits < 1)
@@ -311,6 +591,14 @@ IX_API int ix_paged_attention_decode(const void* q, const void* k_cache, const v
   return launch_decode<TA, HDV, FAST>(q, k_cache, v_cache, block_table, kv_len, part_o, part_ml, \
                                       out, S, heads, kvh, page_size, max_blocks, window, scale,  \
                                       splits, stream)
+  if (act_dtype == IX_BF16 && variant == 0 && (hd == 64 || hd == 128)) {
+    if (hd == 128)
+      return launch_decode_mma<128>(q, k_cache, v_cache, block_table, kv_len, part_o, part_ml, out,
+                                    S, heads, kvh, page_size, max_blocks, window, scale, splits,
+                                    stream);
+    return launch_decode_mma<64>(q, k_cache, v_cache, block_table, kv_len, part_o, part_ml, out, S,
+                                 heads, kvh, page_size, max_blocks, window, scale, splits, stream);
+  }
   if (act_dtype == IX_BF16) {
     if (hd == 64) IX_DEC_HD(bf16, 64, true);
     if (hd == 128) IX_DEC_HD(bf16, 128, true);
@@ -324,4 +612,23 @@ IX_API int ix_paged_attention_decode(const void* q, const void* k_cache, const v
   }
 #undef IX_DEC_HD
   return IX_ERR_DTYPE;
+}
+
+IX_API int ix_paged_attention_decode(const void* q, const void* k_cache, const void* v_cache,
+                                     const int* block_table, const int* kv_len, float* part_o,
+                                     float* part_ml, void* out, int act_dtype, int S, int heads,
+                                     int kvh, int hd, int page_size, int max_blocks, int window,
+                                     float scale, int splits, cudaStream_t stream) {
+  return decode_dispatch(q, k_cache, v_cache, block_table, kv_len, part_o, part_ml, out, act_dtype,
+                         S, heads, kvh, hd, page_size, max_blocks, window, scale, splits, 0, stream);
+}
+
+IX_API int ix_paged_attention_decode_scalar(const void* q, const void* k_cache,
+                                            const void* v_cache, const int* block_table,
+                                            const int* kv_len, float* part_o, float* part_ml,
+                                            void* out, int act_dtype, int S, int heads, int kvh,
+                                            int hd, int page_size, int max_blocks, int window,
+                                            float scale, int splits, cudaStream_t stream) {
+  return decode_dispatch(q, k_cache, v_cache, block_table, kv_len, part_o, part_ml, out, act_dtype,
+                         S, heads, kvh, hd, page_size, max_blocks, window, scale, splits, 1, stream);
 }

@@ -359,7 +359,8 @@ _DECODE_HEAD_SIZES = {torch.bfloat16: (64, 128, 256), torch.float32: (64, 128)}
 
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                            block_table: torch.Tensor, kv_len: torch.Tensor, max_kv_len: int,
-                           window: int, scale: float, splits: Optional[int] = None):
+                           window: int, scale: float, splits: Optional[int] = None,
+                           scalar_kernel: bool = False):
     """Split-KV attention for a batch in which sequence s brings the one query q[s]
     at position kv_len[s] - 1."""
     _chk("q", q)
@@ -384,7 +385,8 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     if splits > 1:
         part_o = torch.empty((S, heads, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((S, heads, splits, 2), dtype=torch.float32, device=q.device)
-    code = lib.ix_paged_attention_decode(
+    entry = lib.ix_paged_attention_decode_scalar if scalar_kernel else lib.ix_paged_attention_decode
+    code = entry(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
         _ptr(part_ml), _ptr(out), _dtype_code(q), S, heads, kvh, hd, page, block_table.shape[1],
         window, ctypes.c_float(scale), splits, _stream())

@@ -52,6 +52,7 @@ class MoeFeedForward:
         self.router_w = self.expert_gate_up = self.expert_down = None
         self.shared = None
         self.shared_gate_w = None
+        self._side = None
         if spec.shared_intermediate > 0:
             from .specs import SwiGluSpec
             self.shared = SwiGluFeedForward(
@@ -91,14 +92,33 @@ class MoeFeedForward:
             if s.shared_gated:
                 self.shared_gate_w = w[f"{p}.shared_expert_gate.weight"].reshape(-1).contiguous()
 
+    # Below this many tokens a step's kernels leave the GPU partly idle; the shared
+    # expert (which needs nothing from the router) then runs beside the routed experts.
+    OVERLAP_MAX_TOKENS = 256
+
+    def _side_stream(self):
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.ctx.device)
+        return self._side
+
     def forward(self, x, step=None):
         s, ops = self.spec, self.ctx.ops
+        shared, side = None, None
+        if self.shared is not None and x.is_cuda and x.shape[0] <= self.OVERLAP_MAX_TOKENS:
+            side = self._side_stream()
+            main = torch.cuda.current_stream(x.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                shared = self.shared.forward(x)
         topk_w, topk_idx, shared_logit = ops.router_topk(
             x, self.router_w, s.top_k, s.renormalize, s.routed_scale, extra_w=self.shared_gate_w)
         offsets, rows, dest = ops.moe_dispatch(topk_idx, s.num_experts)
         act = ops.grouped_gate_up_swiglu(x, rows, offsets, self.expert_gate_up)
         y = ops.grouped_down(act, offsets, self.expert_down)
-        shared = self.shared.forward(x) if self.shared is not None else None
+        if side is not None:
+            main.wait_stream(side)
+        elif self.shared is not None:
+            shared = self.shared.forward(x)
         return ops.moe_combine(y, dest, topk_w, shared, shared_logit)
 
 

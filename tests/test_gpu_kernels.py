@@ -322,7 +322,8 @@ def test_cpu_tensor_is_refused():
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kvh,hd,page,window,splits", [
     (4, 4, 128, 16, 0, None), (8, 2, 64, 8, 0, 3), (6, 3, 128, 16, 50, None),
-    (16, 2, 64, 4, 0, 1), (3, 1, 128, 16, 7, 5), (2, 2, 256, 16, 0, None)])
+    (16, 2, 64, 4, 0, 1), (3, 1, 128, 16, 7, 5), (2, 2, 256, 16, 0, None),
+    (40, 2, 64, 16, 0, 2), (5, 5, 128, 12, 0, None)])
 def test_paged_attention_decode(dtype, heads, kvh, hd, page, window, splits):
     ops = _ops()
     if dtype == torch.float32 and hd == 256:
@@ -332,11 +333,13 @@ def test_paged_attention_decode(dtype, heads, kvh, hd, page, window, splits):
                                              [1] * len(seq_lens), seed=hd)
     kv_len = torch.tensor(seq_lens, dtype=torch.int32)
     scale = 1.0 / math.sqrt(hd)
-    out = ops.paged_attention_decode(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), kv_len.cuda(),
-                                     max(seq_lens), window, scale, splits=splits)
     ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, window, scale)
     tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)
-    torch.testing.assert_close(out.cpu().float(), ref.float(), **tol)
+    for scalar in (False, True):      # the tensor-core kernel (bf16, hd 64/128) and the scalar one
+        out = ops.paged_attention_decode(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), kv_len.cuda(),
+                                         max(seq_lens), window, scale, splits=splits,
+                                         scalar_kernel=scalar)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), **tol)
 
 
 def test_decode_attention_finds_one_far_key():
