@@ -93,6 +93,7 @@ class Executor:
         self.steps_run = 0
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
         self._graphs: Dict[Tuple, _Graph] = {}
+        self._warm = set()
         self.graph_replays = 0
         self.last_h2d_bytes = 0
 
@@ -228,6 +229,16 @@ class Executor:
         wanted = tuple(lay.segs[7])
         key = (lay.S, tuple(lay.widths), wanted)
         slot = self._graphs.get(key)
+        if slot is None and key not in self._warm:
+            # The first step of a shape runs eagerly: kernels are loaded, attributes set
+            # and the library's plans made outside of any capture.  The second is captured.
+            self._warm.add(key)
+            host = torch.zeros(lay.total, dtype=torch.int32).pin_memory()
+            self._fill(host, lay)
+            dev = host.to(self.device, non_blocking=True)
+            self.last_h2d_bytes = lay.total * 4
+            ctx, rows = self._context(dev, lay, static=True)
+            return self.model.forward(ctx, self.caches, rows)
         if slot is None:
             host = torch.zeros(lay.total, dtype=torch.int32).pin_memory()
             dev = torch.zeros(lay.total, dtype=torch.int32, device=self.device)

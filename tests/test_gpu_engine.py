@@ -33,7 +33,7 @@ def test_long_decoding_with_graphs(tmp_path, dtype, cfg, seed, page):
     sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=page, use_graphs=True)
     rows = mc.run_trace(sess, steps)
     assert len(rows) == 330
-    assert sess.executor.graph_replays == 300 and len(sess.executor._graphs) >= 3
+    assert sess.executor.graph_replays >= 290 and len(sess.executor._graphs) >= 3
     mc.compare(rows, ref, REL[dtype], f"long decode {dtype}")
 
 
