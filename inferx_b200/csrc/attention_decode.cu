@@ -561,12 +561,14 @@ static int launch_decode_mma(const void* q, const void* kc, const void* vc, cons
 
 // The number of splits a caller should provide scratch for.
 IX_API int ix_attn_decode_splits(int S, int heads, int kvh, int max_kv_len) {
+  // One wave: two blocks fit on each of the 148 SMs, so aim for at most 296 blocks and
+  // let each of them walk a long range of keys; a grid a little larger than a wave
+  // would leave most SMs idle during its last wave.
   const int rep = heads / (kvh > 0 ? kvh : 1);
-  const int G = rep % 8 == 0 ? 8 : (rep % 4 == 0 ? 4 : (rep % 2 == 0 ? 2 : 1));
-  const long long base = (long long)S * kvh * (rep / G);
-  const int target = 148 * 6;
-  long long splits = (target + base - 1) / base;
-  const int max_by_len = (max_kv_len + 255) / 256;
+  const long long base = (long long)S * kvh * ((rep + 15) / 16);
+  const int slots = 148 * 2;
+  long long splits = base >= slots ? 1 : slots / base;
+  const int max_by_len = (max_kv_len + 127) / 128;   // at least two 64-key tiles per block
   if (splits > max_by_len) splits = max_by_len;
   if (splits > 64) splits = 64;
   if (splits < 1) splits = 1;

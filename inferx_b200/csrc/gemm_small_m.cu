@@ -48,7 +48,7 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, unsigned a0, unsigned a
 }
 
 template <typename TO, bool DUAL, int NT, int KSPLIT>
-__global__ void __launch_bounds__(SM_THREADS, (KSPLIT == 1 || NT >= 4) ? 1 : 2)
+__global__ void __launch_bounds__(SM_THREADS, (NT >= 4 || (NT >= 2 && KSPLIT == 1)) ? 1 : 2)
 gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
                     const int* __restrict__ offsets, const bf16* __restrict__ w,
                     TO* __restrict__ out, int M_single, int N, int K, long long w_expert_stride) {

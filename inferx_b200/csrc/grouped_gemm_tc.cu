@@ -37,6 +37,10 @@
 #define TC_THREADS 192
 #define TC_TILE_BYTES (TC_BM * TC_BK * 2)   // 16 KB: one 128 x 64 bf16 tile
 #define TC_WAIT_POLLS 4000000               // bounded waits: about a second at worst
+// two blocks per SM (96 KB of stages each), so that one block's epilogue and set-up
+// overlap the other's MMA work
+#define TC_STAGES_DUAL 2
+#define TC_STAGES_PLAIN 3
 
 enum { TC_ERR_PRODUCER = 1, TC_ERR_MMA = 2, TC_ERR_EPILOGUE = 3 };
 
@@ -145,7 +149,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_w,
                        const int* __restrict__ offsets, bf16* __restrict__ out, int N, int K,
                        int E, int w_rows_per_expert, int* __restrict__ status) {
-  constexpr int STAGES = DUAL ? 4 : 6;
+  constexpr int STAGES = DUAL ? TC_STAGES_DUAL : TC_STAGES_PLAIN;
   constexpr int STAGE_BYTES = TC_TILE_BYTES * (DUAL ? 3 : 2);
   constexpr unsigned TMEM_COLS = DUAL ? 256 : 128;
   extern __shared__ unsigned char smem_raw[];
@@ -380,14 +384,14 @@ IX_API int ix_grouped_gemm_tc(const void* a, const int* offsets, const void* w, 
   if (m_tiles > 65535) return IX_ERR_SIZE;
   dim3 grid((N + TC_BN - 1) / TC_BN, m_tiles);
   if (dual) {
-    const int smem = 4 * TC_TILE_BYTES * 3 + 1024;
+    const int smem = TC_STAGES_DUAL * TC_TILE_BYTES * 3 + 1024;
     auto kern = grouped_gemm_tc_kernel<true>;
     cudaError_t e2 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e2 != cudaSuccess) return (int)e2;
     kern<<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, offsets, (bf16*)out, N, K, E,
                                              (int)w_rows, status);
   } else {
-    const int smem = 6 * TC_TILE_BYTES * 2 + 1024;
+    const int smem = TC_STAGES_PLAIN * TC_TILE_BYTES * 2 + 1024;
     auto kern = grouped_gemm_tc_kernel<false>;
     cudaError_t e2 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e2 != cudaSuccess) return (int)e2;

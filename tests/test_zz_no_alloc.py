@@ -67,14 +67,16 @@ def test_noalloc_entry_matches_ordinary_entry_twice():
 
 
 def test_noalloc_entry_refuses_what_does_not_fit():
+    """8 sequences x 64 heads x 9 splits x (256 + 2) floats of partials is more than the
+    built-in 2^20 floats.  All tensors are real and large enough, so whatever the
+    entry point decides, nothing reads or writes out of bounds."""
     from inferx_b200.kernels import library
     lib = library.load()
-    # 64 sequences x 64 heads x 16 splits x (256 + 2) floats is far beyond 2^20
-    q, kc, vc, bt, kv_len = _case(5, 2, 4, 4, 64, 8, [40, 9])
-    fn = lib.ix_paged_attention_decode_noalloc
-    fn.restype = ctypes.c_int
-    p = lambda t: ctypes.c_void_p(t.data_ptr())
-    rc = fn(p(q), p(kc), p(vc), p(bt), p(kv_len), p(q), 1, 64, 64, 1, 256, 8, bt.shape[1], 0,
-            ctypes.c_float(1.0), 100000, ctypes.c_void_p(0))
-    assert rc == -6   # IX_ERR_SCRATCH_TOO_SMALL; nothing was launched
+    S, heads, kvh, hd, page = 8, 64, 1, 256, 16
+    lens = [1200] * S
+    q, kc, vc, bt, kv_len = _case(5, S, heads, kvh, hd, page, lens)
+    splits = lib.ix_attn_decode_splits(S, heads, kvh, max(lens))
+    assert S * heads * splits * (hd + 2) > (1 << 20), "sizes no longer exceed the scratch"
+    rc, out = _call_noalloc(lib, q, kc, vc, bt, kv_len, max(lens), 0, 1.0)
     torch.cuda.synchronize()
+    assert rc == -6   # IX_ERR_SCRATCH_TOO_SMALL; nothing was launched
