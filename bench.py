@@ -276,40 +276,46 @@ def time_prefill(rt, tokens, reps, warmup):
 
 def time_e2e(cfg, batch, context, steps, warmup):
     """Decode through the public entry point: host ids in (pinned staging), sampled
-    ids back to the host, every step."""
+    ids back to the host, every step.  Requests are given more tokens to generate than
+    the run needs, so the batch stays whole; the first decode steps of a shape (one
+    eager, one captured) count as warm-up."""
     import torch
     from inferx_b200 import Engine, EngineConfig, SamplingParams
-    total_new = warmup + steps + 2
-    prompt_len = context - total_new
+    warm = warmup + 3
+    slack = 64                      # prompts finish prefill at different steps
+    prompt_len = context - (warm + steps + slack // 2)
     eng = Engine.create(EngineConfig(
-        config_json=cfg, dtype="bfloat16", max_num_seqs=batch, max_model_len=context + 8,
+        config_json=cfg, dtype="bfloat16", max_num_seqs=batch, max_model_len=context + slack + 8,
         max_num_batched_tokens=4096, block_size=16,
-        num_gpu_blocks_override=batch * (-(-(context + 8) // 16) + 1)))
+        num_gpu_blocks_override=batch * (-(-(context + slack + 8) // 16) + 1)))
     g = torch.Generator().manual_seed(11)
     for r in range(batch):
         eng.submit(torch.randint(0, cfg["vocab_size"], (prompt_len,), generator=g).tolist(),
-                   SamplingParams(max_tokens=total_new, ignore_eos=True))
-    # prefill until every request decodes
+                   SamplingParams(max_tokens=warm + steps + slack, ignore_eos=True))
     guard = 0
     while any(s.pending() != 1 for s in eng.scheduler.running) or eng.scheduler.waiting \
-            or not eng.scheduler.running:
+            or len(eng.scheduler.running) < batch:
         eng.step()
         guard += 1
         assert guard < 10000
-    for _ in range(warmup):
+    for _ in range(warm):
         eng.step()
     torch.cuda.synchronize()
+    r0 = eng.runtime.executor.graph_replays
     t0 = time.perf_counter()
     n = 0
     for _ in range(steps):
         n += len(eng.step())
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    assert n == batch * steps, "a request left the batch during the timed region"
     h2d = eng.runtime.executor.last_h2d_bytes
+    replays = eng.runtime.executor.graph_replays - r0
     del eng
     torch.cuda.empty_cache()
-    return {"value": n / dt, "unit": "tok/s", "h2d_bytes_per_step": h2d,
-            "d2h_bytes_per_step": 4 * batch, "ms_per_step": dt / steps * 1e3}
+    return {"value": round(n / dt, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": 4 * batch, "ms_per_step": round(dt / steps * 1e3, 4),
+            "graph_replays": replays}
 
 
 def breakdown(rt, batch, context, steps, prefill_tokens=0):

@@ -230,6 +230,7 @@ template <typename TA, bool FAST>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o,
                                          const float* __restrict__ part_ml, TA* __restrict__ out,
                                          int hd, int splits) {
+  IX_PDL_WAIT();
   const size_t hrow = blockIdx.x;   // s * heads + h
   const float* ml = part_ml + hrow * splits * 2;
   float M = -INFINITY;
@@ -338,6 +339,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
   unsigned char* Vs = Ks + DM_STAGES * TILE_BYTES;           // [STAGES][64][HD]
   __shared__ float sm_m[DEC_WARPS][16];
   __shared__ float sm_l[DEC_WARPS][16];
+  IX_PDL_WAIT();
 
   const int split = blockIdx.x, s = blockIdx.z;
   const int rep = heads / kvh;
@@ -541,21 +543,21 @@ static int launch_decode_mma(const void* q, const void* kc, const void* vc, cons
     auto kern = attn_decode_mma_kernel<HD, true>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    kern<<<grid, DEC_THREADS, smem, stream>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, bt,
-                                              kv_len, part_o, part_ml, (bf16*)out, heads, kvh,
-                                              page_size, page_shift, maxb, window, sl2, splits);
+    ix_launch(kern, grid, dim3(DEC_THREADS), smem, stream, (const bf16*)q, (const bf16*)kc,
+              (const bf16*)vc, bt, kv_len, part_o, part_ml, (bf16*)out, heads, kvh, page_size,
+              page_shift, maxb, window, sl2, splits);
   } else {
     auto kern = attn_decode_mma_kernel<HD, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    kern<<<grid, DEC_THREADS, smem, stream>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, bt,
-                                              kv_len, part_o, part_ml, (bf16*)out, heads, kvh,
-                                              page_size, page_shift, maxb, window, sl2, splits);
+    ix_launch(kern, grid, dim3(DEC_THREADS), smem, stream, (const bf16*)q, (const bf16*)kc,
+              (const bf16*)vc, bt, kv_len, part_o, part_ml, (bf16*)out, heads, kvh, page_size,
+              page_shift, maxb, window, sl2, splits);
   }
   int rc = ix_launch_status();
   if (rc != 0 || splits == 1) return rc;
-  attn_decode_merge_kernel<bf16, true><<<S * heads, HD >= 128 ? 128 : 64, 0, stream>>>(
-      part_o, part_ml, (bf16*)out, HD, splits);
+  ix_launch(attn_decode_merge_kernel<bf16, true>, dim3(S * heads), dim3(HD >= 128 ? 128 : 64), 0,
+            stream, (const float*)part_o, (const float*)part_ml, (bf16*)out, HD, splits);
   return ix_launch_status();
 }
 

@@ -9,6 +9,12 @@
 #include "common.cuh"
 #include "elementwise_vec.cuh"
 
+IX_API int ix_dependent_launch_flag(int set_to) {
+  static int flag = 0;
+  if (set_to >= 0) flag = set_to ? 1 : 0;
+  return flag;
+}
+
 // ---------------------------------------------------------------------------
 // embedding: out[t, :] = table[ids[t], :] widened to fp32 (the residual stream)
 // ---------------------------------------------------------------------------
@@ -25,6 +31,7 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
 
 __global__ void embed_bf16_vec_kernel(const uint4* __restrict__ table, const int* __restrict__ ids,
                                       float4* __restrict__ out, int chunks, int V) {
+  IX_PDL_WAIT();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= V) id = 0;
@@ -44,8 +51,8 @@ IX_API int ix_embed(const void* table, int table_dtype, const int* ids, int T, i
   if (H <= 0 || V <= 0) return IX_ERR_SIZE;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == IX_BF16 && H % 8 == 0 && (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
-    embed_bf16_vec_kernel<<<T, threads, 0, stream>>>((const uint4*)table, ids, (float4*)out, H / 8,
-                                                     V);
+    ix_launch(embed_bf16_vec_kernel, dim3(T), dim3(threads), 0, stream, (const uint4*)table, ids,
+              (float4*)out, H / 8, V);
     return ix_launch_status();
   }
   IX_DISPATCH_DTYPE(table_dtype, TW,
@@ -96,6 +103,7 @@ __global__ void add_rmsnorm_bf16_vec_kernel(float* __restrict__ resid, const bf1
                                             const int* __restrict__ rows, bf16* __restrict__ out,
                                             int H, float eps, int write_resid) {
   __shared__ float scratch[32];
+  IX_PDL_WAIT();
   const int r = blockIdx.x;
   const size_t src = rows ? (size_t)rows[r] : (size_t)r;
   float4* x = reinterpret_cast<float4*>(resid + src * H);
@@ -156,14 +164,14 @@ IX_API int ix_add_rmsnorm(float* resid, const void* delta, const float* gain, co
     const int ni = (chunks + vt - 1) / vt;
     if (ni <= 4) {
       if (ni == 1)
-        add_rmsnorm_bf16_vec_kernel<1><<<R, vt, 0, stream>>>(resid, (const bf16*)delta, gain, rows,
-                                                             (bf16*)out, H, eps, write_resid);
+        ix_launch(add_rmsnorm_bf16_vec_kernel<1>, dim3(R), dim3(vt), 0, stream, resid,
+                  (const bf16*)delta, gain, rows, (bf16*)out, H, eps, write_resid);
       else if (ni == 2)
-        add_rmsnorm_bf16_vec_kernel<2><<<R, vt, 0, stream>>>(resid, (const bf16*)delta, gain, rows,
-                                                             (bf16*)out, H, eps, write_resid);
+        ix_launch(add_rmsnorm_bf16_vec_kernel<2>, dim3(R), dim3(vt), 0, stream, resid,
+                  (const bf16*)delta, gain, rows, (bf16*)out, H, eps, write_resid);
       else
-        add_rmsnorm_bf16_vec_kernel<4><<<R, vt, 0, stream>>>(resid, (const bf16*)delta, gain, rows,
-                                                             (bf16*)out, H, eps, write_resid);
+        ix_launch(add_rmsnorm_bf16_vec_kernel<4>, dim3(R), dim3(vt), 0, stream, resid,
+                  (const bf16*)delta, gain, rows, (bf16*)out, H, eps, write_resid);
       return ix_launch_status();
     }
   }
@@ -254,6 +262,7 @@ __global__ void moe_combine_bf16_vec_kernel(const uint4* __restrict__ y, const i
                                             const uint4* __restrict__ shared,
                                             const float* __restrict__ shared_logit,
                                             uint4* __restrict__ out, int chunks, int k) {
+  IX_PDL_WAIT();
   const int t = blockIdx.x;
   float sg = 1.0f;
   if (shared && shared_logit) sg = 1.0f / (1.0f + expf(-shared_logit[t]));
@@ -287,8 +296,8 @@ IX_API int ix_moe_combine(const void* y, const int* dest, const float* w, const 
   const int threads = H >= 1024 ? 256 : 128;
   if (act_dtype == IX_BF16 && H % 8 == 0 &&
       (((uintptr_t)y | (uintptr_t)shared | (uintptr_t)out) & 15) == 0) {
-    moe_combine_bf16_vec_kernel<<<T, H >= 2048 ? 256 : 128, 0, stream>>>(
-        (const uint4*)y, dest, w, (const uint4*)shared, shared_logit, (uint4*)out, H / 8, k);
+    ix_launch(moe_combine_bf16_vec_kernel, dim3(T), dim3(H >= 2048 ? 256 : 128), 0, stream,
+              (const uint4*)y, dest, w, (const uint4*)shared, shared_logit, (uint4*)out, H / 8, k);
     return ix_launch_status();
   }
   IX_DISPATCH_DTYPE(act_dtype, TA,

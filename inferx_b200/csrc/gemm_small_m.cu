@@ -58,6 +58,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
   constexpr int D = KSPLIT == 1 ? (DUAL ? 4 : (NT >= 4 ? 4 : 8)) : (DUAL ? 2 : (NT >= 4 ? 2 : 4));
   __shared__ float red[KSPLIT > 1 ? (DUAL ? 2 : 1) : 1][KSPLIT > 1 ? SM_WARPS : 1]
                       [KSPLIT > 1 ? NT : 1][4][32];
+  IX_PDL_WAIT();
   const int e = blockIdx.y;
   int lo, hi;
   if (offsets) {
@@ -186,8 +187,9 @@ static int launch_small_m2(const void* x, const int* rows, const int* offsets, c
   const long long w_rows = DUAL ? 2LL * N : N;
   constexpr int TILES = SM_WARPS / KSPLIT;
   dim3 grid((N + 16 * TILES - 1) / (16 * TILES), E);
-  gemm_small_m_kernel<TO, DUAL, NT, KSPLIT><<<grid, SM_THREADS, 0, stream>>>(
-      (const bf16*)x, rows, offsets, (const bf16*)w, (TO*)out, offsets ? 0 : M, N, K, w_rows * K);
+  ix_launch(gemm_small_m_kernel<TO, DUAL, NT, KSPLIT>, grid, dim3(SM_THREADS), 0, stream,
+            (const bf16*)x, rows, offsets, (const bf16*)w, (TO*)out, offsets ? 0 : M, N, K,
+            w_rows * K);
   return ix_launch_status();
 }
 

@@ -96,6 +96,7 @@ qkv_rope_append_bf16_vec_kernel(const bf16* __restrict__ qkv, const float* __res
                                 int page_size, bf16* __restrict__ k_out, bf16* __restrict__ v_out,
                                 int heads, int kvh, int hd) {
   extern __shared__ float trig[];
+  IX_PDL_WAIT();
   const int t = blockIdx.x;
   const int half = rot >> 1;
   float* cs = trig;
@@ -194,9 +195,10 @@ IX_API int ix_qkv_rope_append(const void* qkv, const float* bias, const int* pos
   if (act_dtype == IX_BF16 && hd % 8 == 0 && rot % 16 == 0 && (all & 15) == 0) {
     const int items = (heads + kvh) * (rot / 16 + (hd - rot) / 8) + kvh * (hd / 8);
     const int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
-    qkv_rope_append_bf16_vec_kernel<<<T, threads, smem, stream>>>(
-        (const bf16*)qkv, bias, positions, inv_freq, rot, slots, (bf16*)q_out, (bf16*)k_cache,
-        (bf16*)v_cache, page_size, (bf16*)k_out, (bf16*)v_out, heads, kvh, hd);
+    ix_launch(qkv_rope_append_bf16_vec_kernel, dim3(T), dim3(threads), smem, stream,
+              (const bf16*)qkv, bias, positions, inv_freq, rot, slots, (bf16*)q_out,
+              (bf16*)k_cache, (bf16*)v_cache, page_size, (bf16*)k_out, (bf16*)v_out, heads, kvh,
+              hd);
     return ix_launch_status();
   }
   IX_DISPATCH_DTYPE(act_dtype, TA,

@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS)
 router_logits_kernel(const TA* __restrict__ x, const float* __restrict__ w,
                      const float* __restrict__ extra_w, int T, int H, int E,
                      float* __restrict__ logits, float* __restrict__ extra_out) {
+  IX_PDL_WAIT();
   const int lane = threadIdx.x & 31;
   const int pair = blockIdx.x * (ROUTER_THREADS / 32) + (threadIdx.x >> 5);
   const int rows_total = E + (extra_w ? 1 : 0);
@@ -161,6 +162,7 @@ __global__ void __launch_bounds__(32)
 router_select_kernel(const float* __restrict__ logits, int E, int k, int renorm, float scale,
                      float* __restrict__ topk_w, int* __restrict__ topk_idx) {
   extern __shared__ float prob[];
+  IX_PDL_WAIT();
   const int t = blockIdx.x, lane = threadIdx.x;
   for (int e = lane; e < E; e += 32) prob[e] = logits[(size_t)t * E + e];
   __syncwarp();
@@ -179,12 +181,13 @@ IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, i
     const long long pairs = (long long)T * (E + (extra_w ? 1 : 0));
     const int blocks = (int)((pairs + ROUTER_THREADS / 32 - 1) / (ROUTER_THREADS / 32));
     IX_DISPATCH_DTYPE(act_dtype, TA,
-                      (router_logits_kernel<TA><<<blocks, ROUTER_THREADS, 0, stream>>>(
-                          (const TA*)x, w, extra_w, T, H, E, logits_scratch, extra_out)));
+                      (ix_launch(router_logits_kernel<TA>, dim3(blocks), dim3(ROUTER_THREADS), 0,
+                                 stream, (const TA*)x, w, extra_w, T, H, E, logits_scratch,
+                                 extra_out)));
     int rc = ix_launch_status();
     if (rc != 0) return rc;
-    router_select_kernel<<<T, 32, (size_t)E * sizeof(float), stream>>>(
-        logits_scratch, E, k, renorm, scale, topk_w, topk_idx);
+    ix_launch(router_select_kernel, dim3(T), dim3(32), (size_t)E * sizeof(float), stream,
+              (const float*)logits_scratch, E, k, renorm, scale, topk_w, topk_idx);
     return ix_launch_status();
   }
   // many tokens share one pass over the router weights; few tokens spread out
@@ -216,6 +219,7 @@ __global__ void __launch_bounds__(1024)
 moe_dispatch_kernel(const int* __restrict__ topk_idx, int A, int E, int k,
                     int* __restrict__ offsets, int* __restrict__ rows, int* __restrict__ dest) {
   extern __shared__ int counts[];  // [E + 1]
+  IX_PDL_WAIT();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nwarps = blockDim.x >> 5;
   for (int e = warp; e < E; e += nwarps) {
@@ -346,7 +350,7 @@ IX_API int ix_moe_dispatch(const int* topk_idx, int T, int E, int k, int* offset
     return ix_launch_status();
   }
   const int threads = E >= 32 ? 1024 : 32 * E;
-  moe_dispatch_kernel<<<1, threads, (E + 1) * sizeof(int), stream>>>(topk_idx, A, E, k, offsets,
-                                                                    rows, dest);
+  ix_launch(moe_dispatch_kernel, dim3(1), dim3(threads), (E + 1) * sizeof(int), stream, topk_idx,
+            A, E, k, offsets, rows, dest);
   return ix_launch_status();
 }

@@ -44,6 +44,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   __shared__ float csum[SAMPLE_THREADS];
   __shared__ int s_chunk;
   __shared__ float s_base;
+  IX_PDL_WAIT();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * V;
   const float t = temperature ? temperature[r] : 0.f;
@@ -175,7 +176,7 @@ IX_API int ix_sample(const float* logits, int R, int V, const float* temperature
                      const unsigned long long* seeds, int* out, cudaStream_t stream) {
   if (R <= 0) return IX_OK;
   if (V <= 0) return IX_ERR_SIZE;
-  sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, top_p, top_k, min_p,
-                                                  seeds, out);
+  ix_launch(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, logits, V, temperature,
+            top_p, top_k, min_p, seeds, out);
   return ix_launch_status();
 }

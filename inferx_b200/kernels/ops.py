@@ -88,6 +88,15 @@ def _count(n: int = 1):
     LAUNCHES[0] += n
 
 
+DEPENDENT_LAUNCH_MAX_TOKENS = 16
+
+
+def set_dependent_launch(on: bool) -> None:
+    """Let the kernels of the coming launches start while their predecessor drains
+    (programmatic dependent launch).  Worth it for steps of a few tokens."""
+    _lib().ix_dependent_launch_flag(1 if on else 0)
+
+
 # ---------------------------------------------------------------------------
 def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None):
     """out[t] = table[ids[t]] widened to fp32 (the residual stream)."""

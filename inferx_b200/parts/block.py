@@ -100,6 +100,8 @@ class DecoderModel:
         """Runs the batch; returns fp32 logits [R, vocab] for ``logit_rows`` (token
         indices into the batch), or None when no logits are wanted."""
         ops = self.ctx.ops
+        if hasattr(ops, "set_dependent_launch"):
+            ops.set_dependent_launch(step.num_tokens <= ops.DEPENDENT_LAUNCH_MAX_TOKENS)
         resid = ops.embed(self.embed, step.token_ids)
         pending = None
         for entry, cache in zip(self.spec.schedule, caches):
