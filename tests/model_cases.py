@@ -20,8 +20,20 @@ def sharpen(name, t):
     return t
 
 
+def sharpen_wide(name, t):
+    """The same idea at hidden size 2048, where the tiny models' factors would make
+    attention an argmax that bfloat16 rounding flips: scores and router logits with a
+    spread of two or three."""
+    if name.endswith(("q_proj.weight", "k_proj.weight")):
+        return t * 1.75
+    if name.endswith("mlp.gate.weight"):
+        return t * 2.0
+    return t
+
+
 def make_model_dir(cfg, path, seed, dtype="float32"):
-    write_random_model(cfg, str(path), seed=seed, dtype=dtype, adjust=sharpen)
+    adjust = sharpen_wide if cfg["hidden_size"] >= 1024 else sharpen
+    write_random_model(cfg, str(path), seed=seed, dtype=dtype, adjust=adjust)
     return str(path)
 
 
@@ -40,6 +52,25 @@ def reference_rows(model_dir, requests):
         for p in range(len(toks)):
             rows[(rid, p)] = lg[p]
     return rows
+
+
+def bf16_bound(model_dir, requests, factor=3.0, floor=5e-3):
+    """Error bound for a bfloat16 engine on this model and these requests, relative to
+    the largest logit: ``factor`` times what rounding every stored activation to
+    bfloat16 costs the plain model itself (fp32 run vs the same run with rounding).
+    Derived, not chosen: a model whose routing or attention is close to a tie has a
+    larger budget, a smooth one a small one."""
+    cfg, w = plain.read_model_folder(model_dir)
+    worst = 0.0
+    for toks in requests.values():
+        a = plain.forward(cfg, w, toks)
+        b = plain.forward(cfg, w, toks, plain.round_bf16)
+        worst = max(worst, float((a - b).abs().max()) / float(a.abs().max()))
+    return max(floor, factor * worst)
+
+
+def bound_for(dtype, model_dir, requests):
+    return 2e-5 if dtype == "float32" else bf16_bound(model_dir, requests)
 
 
 def run_trace(session, steps):

@@ -73,7 +73,22 @@ def layer_window(cfg, i):
 
 # ---------------------------------------------------------------------------
 # parts
+#
+# Every part takes ``rf``, a rounding function applied where an engine that stores
+# activations in a narrower type rounds them (after a norm, a projection, the
+# attention output, an activation, a combine).  The default is the identity: pure
+# fp32.  With ``rf=round_bf16`` the same formulas give what bfloat16 storage alone
+# costs, which is how the error budget of the bfloat16 tests is derived (the
+# reference derives its tolerance the same way, scripts/gen_reference_logits.py:51-55).
 # ---------------------------------------------------------------------------
+def _identity(t):
+    return t
+
+
+def round_bf16(t):
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
 def rmsnorm(x, gain, eps):
     """x * rsqrt(mean(x^2) + eps) * gain  (src/backends/cuda/ops/layers.cu:50-76)."""
     ms = (x * x).sum(dim=-1, keepdim=True) / x.shape[-1]
@@ -118,7 +133,7 @@ def attention(q, k, v, scale, window):
     return out
 
 
-def attention_block(cfg, w, prefix, x, positions, window):
+def attention_block(cfg, w, prefix, x, positions, window, rf=_identity):
     """QKV projection with bias on q, k, v only, rotation after the bias, no bias on
     the output projection (src/model/qwen2.cc:920-1027; layers.cu:485-510)."""
     heads, kvh, hd = cfg["num_attention_heads"], cfg.get("num_key_value_heads",
@@ -126,17 +141,17 @@ def attention_block(cfg, w, prefix, x, positions, window):
     T = x.shape[0]
 
     def proj(name):
-        y = x @ w[f"{prefix}.{name}.weight"].T
+        y = rf(x @ w[f"{prefix}.{name}.weight"].T)
         b = w.get(f"{prefix}.{name}.bias")
         return y + b if b is not None else y
 
     q = proj("q_proj").view(T, heads, hd)
     k = proj("k_proj").view(T, kvh, hd)
-    v = proj("v_proj").view(T, kvh, hd)
+    v = rf(proj("v_proj").view(T, kvh, hd))
     theta = cfg.get("rope_theta", 10000.0)
-    q, k = rope(q, positions, theta), rope(k, positions, theta)
-    o = attention(q, k, v, 1.0 / math.sqrt(hd), window)      # scale: qwen2.cc:890
-    return o.reshape(T, heads * hd) @ w[f"{prefix}.o_proj.weight"].T
+    q, k = rf(rope(q, positions, theta)), rf(rope(k, positions, theta))
+    o = rf(attention(q, k, v, 1.0 / math.sqrt(hd), window))      # scale: qwen2.cc:890
+    return rf(o.reshape(T, heads * hd) @ w[f"{prefix}.o_proj.weight"].T)
 
 
 def silu(g):
@@ -144,11 +159,11 @@ def silu(g):
     return g / (1.0 + torch.exp(-g))
 
 
-def swiglu_mlp(w, prefix, x):
+def swiglu_mlp(w, prefix, x, rf=_identity):
     """down(silu(gate(x)) * up(x)), no biases (qwen2.cc:1042-1048)."""
     g = x @ w[f"{prefix}.gate_proj.weight"].T
     u = x @ w[f"{prefix}.up_proj.weight"].T
-    return (silu(g) * u) @ w[f"{prefix}.down_proj.weight"].T
+    return rf(rf(silu(g) * u) @ w[f"{prefix}.down_proj.weight"].T)
 
 
 def route(logits, k, renorm, scale=1.0):
@@ -178,7 +193,7 @@ def route(logits, k, renorm, scale=1.0):
     return weights * scale, experts
 
 
-def moe_block(cfg, w, prefix, x):
+def moe_block(cfg, w, prefix, x, rf=_identity):
     """Routed experts combined in slot order plus the sigmoid-gated shared expert
     over every token (src/model/moe_ffn.cc:158-367; combine moe.cu:237-255; shared
     expert moe.cu:275-287).  Every expert is evaluated on its tokens only."""
@@ -190,42 +205,42 @@ def moe_block(cfg, w, prefix, x):
         acc = torch.zeros(x.shape[1])
         for s in range(k):
             e = int(experts[t, s])
-            y = swiglu_mlp(w, f"{prefix}.experts.{e}", x[t:t + 1])[0]
+            y = swiglu_mlp(w, f"{prefix}.experts.{e}", x[t:t + 1], rf)[0]
             acc = acc + weights[t, s] * y
         out[t] = acc
     if cfg.get("shared_expert_intermediate_size", 0) > 0:
-        shared = swiglu_mlp(w, f"{prefix}.shared_expert", x)
+        shared = swiglu_mlp(w, f"{prefix}.shared_expert", x, rf)
         gate_w = w.get(f"{prefix}.shared_expert_gate.weight")
         if gate_w is not None:
             g = x @ gate_w.T                                     # [T, 1]
             shared = shared * (1.0 / (1.0 + torch.exp(-g)))
         out = out + shared
-    return out
+    return rf(out)
 
 
-def decoder_layer(cfg, w, i, x, positions):
+def decoder_layer(cfg, w, i, x, positions, rf=_identity):
     """r = x; x = attn(norm(x)) + r; r = x; x = ffn(norm(x)) + r (qwen2.cc:908-1051)."""
     p = f"model.layers.{i}"
     eps = cfg.get("rms_norm_eps", 1e-6)
-    n = rmsnorm(x, w[f"{p}.input_layernorm.weight"], eps)
-    x = x + attention_block(cfg, w, f"{p}.self_attn", n, positions, layer_window(cfg, i))
-    n = rmsnorm(x, w[f"{p}.post_attention_layernorm.weight"], eps)
+    n = rf(rmsnorm(x, w[f"{p}.input_layernorm.weight"], eps))
+    x = x + attention_block(cfg, w, f"{p}.self_attn", n, positions, layer_window(cfg, i), rf)
+    n = rf(rmsnorm(x, w[f"{p}.post_attention_layernorm.weight"], eps))
     if layer_is_sparse(cfg, i):
-        f = moe_block(cfg, w, f"{p}.mlp", n)
+        f = moe_block(cfg, w, f"{p}.mlp", n, rf)
     else:
-        f = swiglu_mlp(w, f"{p}.mlp", n)
+        f = swiglu_mlp(w, f"{p}.mlp", n, rf)
     return x + f
 
 
-def forward(cfg, w, tokens):
+def forward(cfg, w, tokens, rf=_identity):
     """Logits [T, vocab] of a whole sequence (embedding layers.cu:465-481; final norm
     and head qwen2.cc:1059-1066; tied head aliases the embedding qwen2.cc:1333-1341)."""
     ids = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(len(tokens))
     x = w["model.embed_tokens.weight"][ids]
     for i in range(cfg["num_hidden_layers"]):
-        x = decoder_layer(cfg, w, i, x, positions)
-    n = rmsnorm(x, w["model.norm.weight"], cfg.get("rms_norm_eps", 1e-6))
+        x = decoder_layer(cfg, w, i, x, positions, rf)
+    n = rf(rmsnorm(x, w["model.norm.weight"], cfg.get("rms_norm_eps", 1e-6)))
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) \
         else w["lm_head.weight"]
     return n @ head.T

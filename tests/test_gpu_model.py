@@ -18,10 +18,10 @@ from inferx_b200.engine.replay import ReplaySession
 pytestmark = pytest.mark.gpu
 
 CASES = [("A", TINY_A, 0, [5, 9, 17, 40, 3, 70], 4), ("B", TINY_B, 1, [1, 6, 13, 31, 45, 80], 8)]
-# error bounds relative to the largest logit of the request: fp32 differs from the
-# plain implementation only by summation order; bfloat16 rounds every activation
-# to 8 bits of mantissa (2^-9 relative) through a few dozen operations
-REL = {"float32": 2e-5, "bfloat16": 4e-2}
+# Error bounds relative to the largest logit of the request: fp32 differs from the plain
+# implementation only by summation order (2e-5); the bfloat16 bound is derived per model
+# from what bfloat16 storage costs the plain model itself (model_cases.bf16_bound).
+
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -35,7 +35,7 @@ def test_replay_matches_plain(tmp_path, dtype, name, cfg, seed, lengths, page, k
     steps = mc.TRACE_KINDS[kind](reqs)
     sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=page, max_live=4)
     rows = mc.run_trace(sess, steps)
-    worst = mc.compare(rows, ref, REL[dtype], f"{name}/{kind}/{dtype}")
+    worst = mc.compare(rows, ref, mc.bound_for(dtype, d, reqs), f"{name}/{kind}/{dtype}")
     print(f"{name}/{kind}/{dtype}: worst relative error {worst:.3e}")
 
 
@@ -68,4 +68,33 @@ def test_trace_run_program(tmp_path, dtype):
             outs.append(torch.from_numpy(
                 np.fromfile(path, dtype="<f4").reshape(n, cfg["vocab_size"]).copy()))
     rows = traces.collect(steps, outs)
-    mc.compare(rows, ref, REL[dtype], f"trace_run/{dtype}")
+    mc.compare(rows, ref, mc.bound_for(dtype, d, reqs), f"trace_run/{dtype}")
+
+
+MID = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "num_hidden_layers": 2, "hidden_size": 2048, "num_attention_heads": 16,
+    "num_key_value_heads": 16, "head_dim": 128, "num_experts": 60, "num_experts_per_tok": 4,
+    "moe_intermediate_size": 1408, "shared_expert_intermediate_size": 5632,
+    "intermediate_size": 5632, "decoder_sparse_step": 2, "mlp_only_layers": [],
+    "norm_topk_prob": True, "vocab_size": 1000, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "use_sliding_window": True, "sliding_window": 96, "max_window_layers": 1,
+    "tie_word_embeddings": False, "torch_dtype": "bfloat16",
+}
+
+
+def test_layer_sizes_of_the_benchmark_model(tmp_path):
+    """Two layers at the widths the benchmark runs (hidden 2048, 16 heads of 128, 60
+    experts of 1408, shared 5632, dense 5632, a 96-token window): the tuned kernels see
+    their real shapes, prompt-sized and decode-sized, against the plain model."""
+    d = mc.make_model_dir(MID, tmp_path / "m", 3, dtype="bfloat16")
+    reqs = mc.make_requests(MID, [330, 150, 40], 3)
+    ref = mc.reference_rows(d, reqs)
+    bound = mc.bf16_bound(d, reqs)
+    for kind in ("tail", "mixed"):
+        steps = mc.TRACE_KINDS[kind](reqs)
+        sess = ReplaySession(d, "bfloat16", traces.peak_tokens(steps), page_size=16, max_live=4,
+                             use_graphs=True)
+        rows = mc.run_trace(sess, steps)
+        worst = mc.compare(rows, ref, bound, f"mid/{kind}")
+        print(f"mid/{kind}: worst relative error {worst:.3e}")
