@@ -14,6 +14,7 @@
 // offsets[E+1], rows[A] (source token of each grouped row) and dest[A] (grouped
 // row of assignment t*k+slot); inside an expert rows ascend by assignment index.
 #include "common.cuh"
+#include "elementwise_vec.cuh"
 
 #define ROUTER_THREADS 256
 #define ROUTER_MAX_TOK 8
@@ -132,6 +133,117 @@ static int launch_router(const void* x, const float* w, const float* extra_w, in
   return ix_launch_status();
 }
 
+// ---------------------------------------------------------------------------
+// bf16 activations, H a multiple of 8.  The dot product of a (token, expert) pair is
+// formed the same way in both kernels below, so routing does not depend on how many
+// tokens a step has: lane l takes the 8-element chunks l, l+32, ... in order, adds the
+// eight products of a chunk in order, and the lanes are summed by the shuffle tree.
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ void dot8(float& acc, const float* xf, const float4& wa,
+                                     const float4& wb) {
+  acc = fmaf(xf[0], wa.x, acc); acc = fmaf(xf[1], wa.y, acc);
+  acc = fmaf(xf[2], wa.z, acc); acc = fmaf(xf[3], wa.w, acc);
+  acc = fmaf(xf[4], wb.x, acc); acc = fmaf(xf[5], wb.y, acc);
+  acc = fmaf(xf[6], wb.z, acc); acc = fmaf(xf[7], wb.w, acc);
+}
+
+#define ROUTER_VTHREADS 512
+
+template <int ROUTER_VTOK>
+__global__ void __launch_bounds__(ROUTER_VTHREADS)
+router_topk_bf16_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ w,
+                            const float* __restrict__ extra_w, int T, int H, int E, int k,
+                            int renorm, float scale, float* __restrict__ topk_w,
+                            int* __restrict__ topk_idx, float* __restrict__ extra_out) {
+  extern __shared__ __align__(16) unsigned char rsm[];
+  const int chunks = H >> 3;
+  uint4* xs = reinterpret_cast<uint4*>(rsm);                               // [VTOK][chunks]
+  float* lg = reinterpret_cast<float*>(rsm + (size_t)ROUTER_VTOK * chunks * 16);   // [VTOK][E]
+  const int t0 = blockIdx.x * ROUTER_VTOK;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = ROUTER_VTHREADS / 32;
+  for (int idx = threadIdx.x; idx < ROUTER_VTOK * chunks; idx += ROUTER_VTHREADS) {
+    const int tk = idx / chunks, c = idx - tk * chunks;
+    const int t = t0 + tk;
+    xs[idx] = t < T ? reinterpret_cast<const uint4*>(x + (size_t)t * H)[c] : make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  const int rows_total = E + (extra_w ? 1 : 0);
+  for (int e = warp; e < rows_total; e += nwarps) {
+    const float4* wr = reinterpret_cast<const float4*>(e < E ? w + (size_t)e * H : extra_w);
+    float acc[ROUTER_VTOK];
+#pragma unroll
+    for (int tk = 0; tk < ROUTER_VTOK; ++tk) acc[tk] = 0.f;
+    // four chunks of weights are fetched before they are used, so that their latency
+    // overlaps the arithmetic of the previous four
+    for (int c0 = lane; c0 < chunks; c0 += 32 * 4) {
+      float4 wa[4], wb[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * 32;
+        if (c < chunks) {
+          wa[u] = wr[2 * c];
+          wb[u] = wr[2 * c + 1];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * 32;
+        if (c < chunks) {
+#pragma unroll
+          for (int tk = 0; tk < ROUTER_VTOK; ++tk) {
+            float xf[8];
+            bf8_to_f32(xs[tk * chunks + c], xf);
+            dot8(acc[tk], xf, wa[u], wb[u]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int tk = 0; tk < ROUTER_VTOK; ++tk) {
+      const float v = warp_sum(acc[tk]);
+      if (lane == 0) {
+        if (e < E) lg[tk * E + e] = v;
+        else if (t0 + tk < T) extra_out[t0 + tk] = v;
+      }
+    }
+  }
+  __syncthreads();
+  for (int tk = warp; tk < ROUTER_VTOK; tk += nwarps) {
+    const int t = t0 + tk;
+    if (t >= T) continue;
+    select_topk(lg + tk * E, E, k, renorm, scale, topk_w + (size_t)t * k, topk_idx + (size_t)t * k,
+                lane);
+  }
+}
+
+__global__ void __launch_bounds__(ROUTER_THREADS)
+router_logits_bf16_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ w,
+                              const float* __restrict__ extra_w, int T, int H, int E,
+                              float* __restrict__ logits, float* __restrict__ extra_out) {
+  IX_PDL_WAIT();
+  const int lane = threadIdx.x & 31;
+  const int pair = blockIdx.x * (ROUTER_THREADS / 32) + (threadIdx.x >> 5);
+  const int rows_total = E + (extra_w ? 1 : 0);
+  if (pair >= T * rows_total) return;
+  const int t = pair / rows_total, e = pair - t * rows_total;
+  const float4* wr = reinterpret_cast<const float4*>(e < E ? w + (size_t)e * H : extra_w);
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)t * H);
+  const int chunks = H >> 3;
+  float acc = 0.f;
+  for (int c = lane; c < chunks; c += 32) {
+    float xf[8];
+    bf8_to_f32(xr[c], xf);
+    dot8(acc, xf, wr[2 * c], wr[2 * c + 1]);
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    if (e < E) logits[(size_t)t * E + e] = acc;
+    else extra_out[t] = acc;
+  }
+}
+
 // Few tokens: one warp per (token, expert) for the logits, so that the router
 // weights are streamed by many blocks at once, then one warp per token selects.
 // The dot product uses the same lane striding and shuffle tree as the fused
@@ -176,10 +288,21 @@ IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, i
   if (T <= 0) return IX_OK;
   if (H <= 0 || E <= 0 || k <= 0 || k > E || k > ROUTER_MAX_TOPK) return IX_ERR_SIZE;
   if (extra_w && !extra_out) return IX_ERR_SIZE;
+  const bool vec = act_dtype == IX_BF16 && H % 8 == 0 &&
+                   (((uintptr_t)x | (uintptr_t)w | (uintptr_t)extra_w) & 15) == 0;
   if (logits_scratch && T < 2 * 148 && (size_t)E * sizeof(float) <= 48 * 1024) {
     // logits_scratch: [T, E] fp32
     const long long pairs = (long long)T * (E + (extra_w ? 1 : 0));
     const int blocks = (int)((pairs + ROUTER_THREADS / 32 - 1) / (ROUTER_THREADS / 32));
+    if (vec) {
+      ix_launch(router_logits_bf16_vec_kernel, dim3(blocks), dim3(ROUTER_THREADS), 0, stream,
+                (const bf16*)x, w, extra_w, T, H, E, logits_scratch, extra_out);
+      int rc = ix_launch_status();
+      if (rc != 0) return rc;
+      ix_launch(router_select_kernel, dim3(T), dim3(32), (size_t)E * sizeof(float), stream,
+                (const float*)logits_scratch, E, k, renorm, scale, topk_w, topk_idx);
+      return ix_launch_status();
+    }
     IX_DISPATCH_DTYPE(act_dtype, TA,
                       (ix_launch(router_logits_kernel<TA>, dim3(blocks), dim3(ROUTER_THREADS), 0,
                                  stream, (const TA*)x, w, extra_w, T, H, E, logits_scratch,
@@ -189,6 +312,23 @@ IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, i
     ix_launch(router_select_kernel, dim3(T), dim3(32), (size_t)E * sizeof(float), stream,
               (const float*)logits_scratch, E, k, renorm, scale, topk_w, topk_idx);
     return ix_launch_status();
+  }
+  if (vec) {
+    // 16 tokens share one pass over the router weights when there are enough tokens to
+    // fill the device with such blocks; fewer tokens per block otherwise
+    const int vtok = T >= 16 * 128 ? 16 : 4;
+    const size_t smem = (size_t)vtok * (H / 8) * 16 + (size_t)vtok * E * sizeof(float);
+    if (smem <= 200 * 1024) {
+      auto kern = vtok == 16 ? router_topk_bf16_vec_kernel<16> : router_topk_bf16_vec_kernel<4>;
+      if (smem > 48 * 1024) {
+        cudaError_t e2 =
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e2 != cudaSuccess) return (int)e2;
+      }
+      kern<<<(T + vtok - 1) / vtok, ROUTER_VTHREADS, smem, stream>>>(
+          (const bf16*)x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx, extra_out);
+      return ix_launch_status();
+    }
   }
   // many tokens share one pass over the router weights; few tokens spread out
   const size_t per_tok = ((size_t)H + E) * sizeof(float);
@@ -332,7 +472,7 @@ dispatch_place_kernel(const int* __restrict__ topk_idx, int A, int E, int k,
 // single-block kernel.
 IX_API int ix_moe_dispatch_scratch_ints(int T, int E, int k) {
   const long long A = (long long)T * k;
-  if (A <= 2048 || E > DISPATCH_MAX_E) return 0;
+  if (A <= 512 || E > DISPATCH_MAX_E) return 0;
   return (int)(((A + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK) * E);
 }
 
@@ -341,7 +481,7 @@ IX_API int ix_moe_dispatch(const int* topk_idx, int T, int E, int k, int* offset
   if (E <= 0 || k <= 0 || E > 8192) return IX_ERR_SIZE;
   if (T < 0) return IX_ERR_SIZE;
   const int A = T * k;
-  if (scratch && A > 2048 && E <= DISPATCH_MAX_E) {
+  if (scratch && A > 512 && E <= DISPATCH_MAX_E) {
     const int blocks = (A + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK;
     dispatch_count_kernel<<<blocks, DISPATCH_CHUNK, 0, stream>>>(topk_idx, A, E, scratch);
     dispatch_scan_kernel<<<1, DISPATCH_MAX_E, 0, stream>>>(scratch, blocks, E, offsets);

@@ -140,6 +140,24 @@ def dense(args):
             "TFLOPs": round(2 * M * N * K / us / 1e6, 2)}
 
 
+def router(args):
+    from . import ops
+    T, H, E, k = args.tokens, args.hidden, args.experts, args.top_k
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(E, H, device="cuda", dtype=torch.float32) * 0.02
+    extra = torch.randn(H, device="cuda", dtype=torch.float32) * 0.02
+
+    def fn(i):
+        ops.router_topk(x, w, k, False, 1.0, extra_w=extra)
+    us = _time(fn, 1, args.iters)
+    idx = ops.router_topk(x, w, k, False, 1.0, extra_w=extra)[1]
+
+    def fd(i):
+        ops.moe_dispatch(idx, E)
+    return {"case": "router", "tokens": T, "router_us": round(us, 2),
+            "dispatch_us": round(_time(fd, 1, args.iters), 2)}
+
+
 def attn_prefill(args):
     from . import ops
     T, heads, kvh, hd, page = args.tokens, args.heads, args.kv_heads, args.head_dim, args.page
@@ -168,7 +186,7 @@ def attn_prefill(args):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("case", choices=["attn_decode", "grouped", "dense", "attn_prefill"])
+    ap.add_argument("case", choices=["attn_decode", "grouped", "dense", "attn_prefill", "router"])
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)

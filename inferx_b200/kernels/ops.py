@@ -271,7 +271,10 @@ def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, renormalize: bool,
                 ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """fp32 router logits, softmax over all experts, top-k (ties to the lower index).
 
-    Returns (weights [T,k] fp32, experts [T,k] int32, x.extra_w [T] fp32 or None)."""
+    Returns (weights [T,k] fp32, experts [T,k] int32, x.extra_w [T] fp32 or None).
+    Few tokens: one warp per (token, expert) computes the logits and one warp per
+    token selects; many tokens: one fused kernel over 16 tokens per block.  Both form
+    a dot product in the same order, so a token's routing is the same in either."""
     _chk("x", x)
     _chk("w", w, torch.float32)
     _chk("extra_w", extra_w, torch.float32, optional=True)
