@@ -293,7 +293,7 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const in
 // Same scratch layout and merge kernel as the scalar form.
 // ---------------------------------------------------------------------------
 #define DM_BN 64
-#define DM_STAGES 3
+#define DM_STAGES 2
 
 __device__ __forceinline__ void dm_cp16(void* smem, const void* gmem, bool valid) {
   const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
@@ -389,7 +389,6 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
     asm volatile("cp.async.commit_group;");
   };
   load_kv(0);
-  load_kv(1);
 
   float o[DT][4];
 #pragma unroll
@@ -400,8 +399,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
   unsigned qf[KS][4];
 
   for (int it = 0; it < n_tiles; ++it) {
-    load_kv(it + 2);
-    asm volatile("cp.async.wait_group 2;");
+    load_kv(it + 1);
+    asm volatile("cp.async.wait_group 1;");
     __syncthreads();
     if (it == 0) {
 #pragma unroll
@@ -563,12 +562,12 @@ static int launch_decode_mma(const void* q, const void* kc, const void* vc, cons
 
 // The number of splits a caller should provide scratch for.
 IX_API int ix_attn_decode_splits(int S, int heads, int kvh, int max_kv_len) {
-  // One wave: two blocks fit on each of the 148 SMs, so aim for at most 296 blocks and
+  // One wave: three blocks fit on each of the 148 SMs, so aim for at most 444 blocks and
   // let each of them walk a long range of keys; a grid a little larger than a wave
   // would leave most SMs idle during its last wave.
   const int rep = heads / (kvh > 0 ? kvh : 1);
   const long long base = (long long)S * kvh * ((rep + 15) / 16);
-  const int slots = 148 * 2;
+  const int slots = 148 * 3;
   long long splits = base >= slots ? 1 : slots / base;
   const int max_by_len = (max_kv_len + 127) / 128;   // at least two 64-key tiles per block
   if (splits > max_by_len) splits = max_by_len;
