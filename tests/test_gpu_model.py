@@ -83,6 +83,34 @@ MID = {
 }
 
 
+GQA = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "num_hidden_layers": 2, "hidden_size": 1792, "num_attention_heads": 14,
+    "num_key_value_heads": 2, "head_dim": 128, "num_experts": 16, "num_experts_per_tok": 8,
+    "moe_intermediate_size": 320, "shared_expert_intermediate_size": 640,
+    "decoder_sparse_step": 1, "mlp_only_layers": [], "norm_topk_prob": False,
+    "vocab_size": 777, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "use_sliding_window": False, "tie_word_embeddings": True, "torch_dtype": "bfloat16",
+}
+
+
+def test_grouped_query_heads_at_width(tmp_path):
+    """Seven query heads per KV head, head size 128, top-8 routing (the shape family of
+    the larger Qwen2-MoE checkpoints, scaled down in width): the tensor-core attention
+    kernels pack the seven heads of a group into one tile."""
+    d = mc.make_model_dir(GQA, tmp_path / "m", 4, dtype="bfloat16")
+    reqs = mc.make_requests(GQA, [200, 75, 33], 4)
+    ref = mc.reference_rows(d, reqs)
+    bound = mc.bf16_bound(d, reqs)
+    for kind in ("tail", "mixed"):
+        steps = mc.TRACE_KINDS[kind](reqs)
+        sess = ReplaySession(d, "bfloat16", traces.peak_tokens(steps), page_size=16, max_live=4,
+                             use_graphs=(kind == "tail"))
+        rows = mc.run_trace(sess, steps)
+        worst = mc.compare(rows, ref, bound, f"gqa/{kind}")
+        print(f"gqa/{kind}: worst relative error {worst:.3e} (bound {bound:.3e})")
+
+
 def test_layer_sizes_of_the_benchmark_model(tmp_path):
     """Two layers at the widths the benchmark runs (hidden 2048, 16 heads of 128, 60
     experts of 1408, shared 5632, dense 5632, a 96-token window): the tuned kernels see
