@@ -367,6 +367,22 @@ def append_kv(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: 
 
 
 _DECODE_HEAD_SIZES = {torch.bfloat16: (64, 128, 256), torch.float32: (64, 128)}
+_DECODE_COUNTERS = {}
+_DECODE_COUNTER_INTS = 1 << 16
+
+
+def _decode_counters(device, need: int):
+    """A zeroed int32 buffer that the split-KV kernel's blocks count themselves in
+    (the last one merges the splits and puts its entry back to zero).  Made once per
+    device, outside of any stream capture; None when that is not possible."""
+    key = torch.device(device).index or 0
+    buf = _DECODE_COUNTERS.get(key)
+    if buf is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        buf = torch.zeros(_DECODE_COUNTER_INTS, dtype=torch.int32, device=device)
+        _DECODE_COUNTERS[key] = buf
+    return buf if need <= _DECODE_COUNTER_INTS else None
 
 
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -397,13 +413,21 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     if splits > 1:
         part_o = torch.empty((S, heads, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((S, heads, splits, 2), dtype=torch.float32, device=q.device)
-    entry = lib.ix_paged_attention_decode_scalar if scalar_kernel else lib.ix_paged_attention_decode
-    code = entry(
-        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
-        _ptr(part_ml), _ptr(out), _dtype_code(q), S, heads, kvh, hd, page, block_table.shape[1],
-        window, ctypes.c_float(scale), splits, _stream())
+    counters = None
+    if not scalar_kernel and splits > 1 and q.dtype == torch.bfloat16 and hd in (64, 128):
+        counters = _decode_counters(q.device, S * kvh * (-(-(heads // kvh) // 16)))
+    if scalar_kernel:
+        code = lib.ix_paged_attention_decode_scalar(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
+            _ptr(part_ml), _ptr(out), _dtype_code(q), S, heads, kvh, hd, page,
+            block_table.shape[1], window, ctypes.c_float(scale), splits, _stream())
+    else:
+        code = lib.ix_paged_attention_decode_fused(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
+            _ptr(part_ml), _ptr(counters), _ptr(out), _dtype_code(q), S, heads, kvh, hd, page,
+            block_table.shape[1], window, ctypes.c_float(scale), splits, _stream())
     _check(code, "paged_attention_decode")
-    _count(2 if splits > 1 else 1)
+    _count(2 if (splits > 1 and counters is None) else 1)
     return out
 
 
