@@ -330,7 +330,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
                        const int* __restrict__ kv_len, float* __restrict__ part_o,
                        float* __restrict__ part_ml, bf16* __restrict__ out, int heads, int kvh,
                        int page_size, int page_shift, int maxb, int window, float scale_log2e,
-                       int splits, int* __restrict__ counters) {
+                       int splits) {
   constexpr int CH = HD / 8, KS = HD / 16, DT = HD / 8;
   constexpr int TILE_BYTES = DM_BN * HD * 2;
   extern __shared__ __align__(128) unsigned char dsm[];
@@ -523,47 +523,13 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
       }
     }
   }
-  // The block that finishes last for this (sequence, head group) merges the splits,
-  // which saves a second launch.  counters[] is zero between calls: the merging block
-  // puts its entry back to zero.
-  if (splits > 1 && counters != nullptr) {
-    __shared__ int s_last;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const int prev = atomicAdd(&counters[s * gridDim.y + blockIdx.y], 1);
-      s_last = prev == splits - 1;
-    }
-    __syncthreads();
-    if (s_last) {
-      __threadfence();
-      for (int idx = tid; idx < rows_valid * HD; idx += DEC_THREADS) {
-        const int r = idx / HD, d = idx - r * HD;
-        const size_t hrow = (size_t)s * heads + h0 + r;
-        const float* ml = part_ml + hrow * splits * 2;
-        float M = -INFINITY;
-        for (int j = 0; j < splits; ++j) M = fmaxf(M, __ldcg(ml + 2 * j));
-        float ov = 0.f, L = 0.f;
-        for (int j = 0; j < splits; ++j) {
-          const float mj = __ldcg(ml + 2 * j);
-          if (mj != -INFINITY) {
-            const float cj = ix_exp2<true>(mj - M);
-            L += __ldcg(ml + 2 * j + 1) * cj;
-            ov += __ldcg(part_o + (hrow * splits + j) * HD + d) * cj;
-          }
-        }
-        out[hrow * HD + d] = __float2bfloat16_rn(L > 0.f ? ov / L : 0.f);
-      }
-      if (tid == 0) counters[s * gridDim.y + blockIdx.y] = 0;
-    }
-  }
 }
 
 template <int HD>
 static int launch_decode_mma(const void* q, const void* kc, const void* vc, const int* bt,
                              const int* kv_len, float* part_o, float* part_ml, void* out, int S,
                              int heads, int kvh, int page_size, int maxb, int window, float scale,
-                             int splits, int* counters, cudaStream_t stream) {
+                             int splits, cudaStream_t stream) {
   const int rep = heads / kvh;
   const float sl2 = scale * 1.4426950408889634f;
   int page_shift = -1;
@@ -578,17 +544,17 @@ static int launch_decode_mma(const void* q, const void* kc, const void* vc, cons
     if (e != cudaSuccess) return (int)e;
     ix_launch(kern, grid, dim3(DEC_THREADS), smem, stream, (const bf16*)q, (const bf16*)kc,
               (const bf16*)vc, bt, kv_len, part_o, part_ml, (bf16*)out, heads, kvh, page_size,
-              page_shift, maxb, window, sl2, splits, counters);
+              page_shift, maxb, window, sl2, splits);
   } else {
     auto kern = attn_decode_mma_kernel<HD, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     ix_launch(kern, grid, dim3(DEC_THREADS), smem, stream, (const bf16*)q, (const bf16*)kc,
               (const bf16*)vc, bt, kv_len, part_o, part_ml, (bf16*)out, heads, kvh, page_size,
-              page_shift, maxb, window, sl2, splits, counters);
+              page_shift, maxb, window, sl2, splits);
   }
   int rc = ix_launch_status();
-  if (rc != 0 || splits == 1 || counters != nullptr) return rc;
+  if (rc != 0 || splits == 1) return rc;
   ix_launch(attn_decode_merge_kernel<bf16, true>, dim3(S * heads), dim3(HD >= 128 ? 128 : 64), 0,
             stream, (const float*)part_o, (const float*)part_ml, (bf16*)out, HD, splits);
   return ix_launch_status();
@@ -616,7 +582,7 @@ static int decode_dispatch(const void* q, const void* k_cache, const void* v_cac
                            const int* block_table, const int* kv_len, float* part_o,
                            float* part_ml, void* out, int act_dtype, int S, int heads, int kvh,
                            int hd, int page_size, int max_blocks, int window, float scale,
-                           int splits, int variant, int* counters, cudaStream_t stream) {
+                           int splits, int variant, cudaStream_t stream) {
   if (S <= 0) return IX_OK;
   if (heads <= 0 || kvh <= 0 || heads % kvh != 0 || page_size <= 0 || max_blocks <= 0 ||
       window < 0 || splits < 1)
@@ -632,10 +598,9 @@ static int decode_dispatch(const void* q, const void* k_cache, const void* v_cac
     if (hd == 128)
       return launch_decode_mma<128>(q, k_cache, v_cache, block_table, kv_len, part_o, part_ml, out,
                                     S, heads, kvh, page_size, max_blocks, window, scale, splits,
-                                    counters, stream);
+                                    stream);
     return launch_decode_mma<64>(q, k_cache, v_cache, block_table, kv_len, part_o, part_ml, out, S,
-                                 heads, kvh, page_size, max_blocks, window, scale, splits, counters,
-                                 stream);
+                                 heads, kvh, page_size, max_blocks, window, scale, splits, stream);
   }
   if (act_dtype == IX_BF16) {
     if (hd == 64) IX_DEC_HD(bf16, 64, true);
@@ -658,22 +623,7 @@ IX_API int ix_paged_attention_decode(const void* q, const void* k_cache, const v
                                      int kvh, int hd, int page_size, int max_blocks, int window,
                                      float scale, int splits, cudaStream_t stream) {
   return decode_dispatch(q, k_cache, v_cache, block_table, kv_len, part_o, part_ml, out, act_dtype,
-                         S, heads, kvh, hd, page_size, max_blocks, window, scale, splits, 0, nullptr,
-                         stream);
-}
-
-// The same with the merge of the splits done by the last block of the first kernel.
-// counters: at least S * kv_heads * ceil(rep / 16) ints, zero before the first call (the
-// kernel leaves them zero); null selects the separate merge kernel.
-IX_API int ix_paged_attention_decode_fused(const void* q, const void* k_cache, const void* v_cache,
-                                           const int* block_table, const int* kv_len,
-                                           float* part_o, float* part_ml, int* counters, void* out,
-                                           int act_dtype, int S, int heads, int kvh, int hd,
-                                           int page_size, int max_blocks, int window, float scale,
-                                           int splits, cudaStream_t stream) {
-  return decode_dispatch(q, k_cache, v_cache, block_table, kv_len, part_o, part_ml, out, act_dtype,
-                         S, heads, kvh, hd, page_size, max_blocks, window, scale, splits, 0,
-                         counters, stream);
+                         S, heads, kvh, hd, page_size, max_blocks, window, scale, splits, 0, stream);
 }
 
 IX_API int ix_paged_attention_decode_scalar(const void* q, const void* k_cache,
@@ -683,6 +633,5 @@ IX_API int ix_paged_attention_decode_scalar(const void* q, const void* k_cache,
                                             int hd, int page_size, int max_blocks, int window,
                                             float scale, int splits, cudaStream_t stream) {
   return decode_dispatch(q, k_cache, v_cache, block_table, kv_len, part_o, part_ml, out, act_dtype,
-                         S, heads, kvh, hd, page_size, max_blocks, window, scale, splits, 1, nullptr,
-                         stream);
+                         S, heads, kvh, hd, page_size, max_blocks, window, scale, splits, 1, stream);
 }

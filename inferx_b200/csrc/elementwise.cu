@@ -288,6 +288,102 @@ __global__ void moe_combine_bf16_vec_kernel(const uint4* __restrict__ y, const i
   }
 }
 
+// ---------------------------------------------------------------------------
+// The combine above folded into the residual add + RMSNorm that consumes it: the
+// row of routed and shared contributions is formed in registers and never written.
+// ---------------------------------------------------------------------------
+template <int NI>
+__global__ void combine_add_rmsnorm_bf16_vec_kernel(
+    float* __restrict__ resid, const uint4* __restrict__ y, const int* __restrict__ dest,
+    const float* __restrict__ w, const uint4* __restrict__ shared,
+    const float* __restrict__ shared_logit, const float* __restrict__ gain,
+    bf16* __restrict__ out, int H, int k, float eps) {
+  __shared__ float scratch[32];
+  IX_PDL_WAIT();
+  const int t = blockIdx.x;
+  const int chunks = H >> 3;
+  float4* x = reinterpret_cast<float4*>(resid + (size_t)t * H);
+  float sg = 1.0f;
+  if (shared && shared_logit) sg = 1.0f / (1.0f + expf(-shared_logit[t]));
+  float v[NI][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < chunks) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int s = 0; s < k; ++s) {
+        const int row = dest[t * k + s];
+        const float ws = w[t * k + s];
+        float f[8];
+        bf8_to_f32(y[(size_t)row * chunks + c], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += ws * f[j];
+      }
+      if (shared) {
+        float f[8];
+        bf8_to_f32(shared[(size_t)t * chunks + c], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += sg * f[j];
+      }
+      const float4 a = x[2 * c], b = x[2 * c + 1];
+      v[i][0] = a.x + acc[0]; v[i][1] = a.y + acc[1]; v[i][2] = a.z + acc[2];
+      v[i][3] = a.w + acc[3]; v[i][4] = b.x + acc[4]; v[i][5] = b.y + acc[5];
+      v[i][6] = b.z + acc[6]; v[i][7] = b.w + acc[7];
+      x[2 * c] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+      x[2 * c + 1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)H + eps);
+  uint4* o = reinterpret_cast<uint4*>(out + (size_t)t * H);
+  const float4* gw = reinterpret_cast<const float4*>(gain);
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < chunks) {
+      const float4 ga = gw[2 * c], gb = gw[2 * c + 1];
+      float f[8];
+      f[0] = v[i][0] * inv * ga.x; f[1] = v[i][1] * inv * ga.y;
+      f[2] = v[i][2] * inv * ga.z; f[3] = v[i][3] * inv * ga.w;
+      f[4] = v[i][4] * inv * gb.x; f[5] = v[i][5] * inv * gb.y;
+      f[6] = v[i][6] * inv * gb.z; f[7] = v[i][7] * inv * gb.w;
+      o[c] = f32_to_bf8(f);
+    }
+  }
+}
+
+// resid[t] += combine(t); out[t] = RMSNorm(resid[t]) * gain.  bf16, H a multiple of 8 up
+// to 8192; anything else is refused and the caller runs the two kernels.
+IX_API int ix_combine_add_rmsnorm(float* resid, const void* y, const int* dest, const float* w,
+                                  const void* shared, const float* shared_logit,
+                                  const float* gain, void* out, int T, int H, int k, float eps,
+                                  cudaStream_t stream) {
+  if (T <= 0) return IX_OK;
+  if (H <= 0 || k <= 0) return IX_ERR_SIZE;
+  if (H % 8 != 0) return IX_ERR_UNSUPPORTED;
+  if ((((uintptr_t)resid | (uintptr_t)y | (uintptr_t)shared | (uintptr_t)gain | (uintptr_t)out) &
+       15) != 0)
+    return IX_ERR_ALIGN;
+  const int chunks = H / 8;
+  const int vt = chunks >= 256 ? 256 : (chunks >= 128 ? 128 : 64);
+  const int ni = (chunks + vt - 1) / vt;
+  if (ni > 4) return IX_ERR_UNSUPPORTED;
+#define IX_CAR(NI)                                                                           \
+  ix_launch(combine_add_rmsnorm_bf16_vec_kernel<NI>, dim3(T), dim3(vt), 0, stream, resid,     \
+            (const uint4*)y, dest, w, (const uint4*)shared, shared_logit, gain, (bf16*)out, H, k, \
+            eps)
+  if (ni == 1) IX_CAR(1);
+  else if (ni == 2) IX_CAR(2);
+  else IX_CAR(4);
+#undef IX_CAR
+  return ix_launch_status();
+}
+
 IX_API int ix_moe_combine(const void* y, const int* dest, const float* w, const void* shared,
                           const float* shared_logit, void* out, int act_dtype, int T, int H, int k,
                           cudaStream_t stream) {

@@ -113,12 +113,50 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = 
     return out
 
 
-def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor,
+class CombinePending:
+    """The output of a mixture-of-experts block that has not been written yet: the
+    expert rows, where each token's rows are, their weights and the shared expert's
+    part.  ``add_rmsnorm`` consumes it in the same pass that adds it to the residual;
+    ``materialize`` writes it out like ``moe_combine``."""
+
+    def __init__(self, y, dest, topk_w, shared, shared_logit):
+        self.y, self.dest, self.topk_w = y, dest, topk_w
+        self.shared, self.shared_logit = shared, shared_logit
+        self.shape = (topk_w.shape[0], y.shape[1])
+        self.dtype = y.dtype
+
+    def materialize(self):
+        return moe_combine(self.y, self.dest, self.topk_w, self.shared, self.shared_logit)
+
+
+def moe_combine_pending(y, dest, topk_w, shared, shared_logit):
+    """``moe_combine`` deferred into the next residual add + norm where that kernel
+    exists (bfloat16, width a multiple of 8); the combined tensor otherwise."""
+    if y.dtype == torch.bfloat16 and y.shape[1] % 8 == 0 and y.shape[1] <= 8192:
+        return CombinePending(y, dest, topk_w, shared, shared_logit)
+    return moe_combine(y, dest, topk_w, shared, shared_logit)
+
+
+def add_rmsnorm(resid: torch.Tensor, delta, gain: torch.Tensor,
                 eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
     """resid += delta (kept when ``rows`` is None); returns RMSNorm(resid) * gain.
 
     With ``rows`` the listed rows are gathered, normalised and returned without
-    writing the residual back."""
+    writing the residual back.  ``delta`` may be a ``CombinePending``."""
+    if isinstance(delta, CombinePending):
+        if rows is None and out_dtype == torch.bfloat16 and delta.shape == tuple(resid.shape):
+            _chk("resid", resid, torch.float32)
+            _chk("gain", gain, torch.float32)
+            T, H = resid.shape
+            out = torch.empty((T, H), dtype=out_dtype, device=resid.device)
+            code = _lib().ix_combine_add_rmsnorm(
+                _ptr(resid), _ptr(delta.y), _ptr(delta.dest), _ptr(delta.topk_w),
+                _ptr(delta.shared), _ptr(delta.shared_logit), _ptr(gain), _ptr(out), T, H,
+                delta.topk_w.shape[1], ctypes.c_float(eps), _stream())
+            _check(code, "combine_add_rmsnorm")
+            _count()
+            return out
+        delta = delta.materialize()
     _chk("resid", resid, torch.float32)
     _chk("gain", gain, torch.float32)
     _chk("delta", delta, optional=True)
@@ -367,22 +405,6 @@ def append_kv(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: 
 
 
 _DECODE_HEAD_SIZES = {torch.bfloat16: (64, 128, 256), torch.float32: (64, 128)}
-_DECODE_COUNTERS = {}
-_DECODE_COUNTER_INTS = 1 << 16
-
-
-def _decode_counters(device, need: int):
-    """A zeroed int32 buffer that the split-KV kernel's blocks count themselves in
-    (the last one merges the splits and puts its entry back to zero).  Made once per
-    device, outside of any stream capture; None when that is not possible."""
-    key = torch.device(device).index or 0
-    buf = _DECODE_COUNTERS.get(key)
-    if buf is None:
-        if torch.cuda.is_current_stream_capturing():
-            return None
-        buf = torch.zeros(_DECODE_COUNTER_INTS, dtype=torch.int32, device=device)
-        _DECODE_COUNTERS[key] = buf
-    return buf if need <= _DECODE_COUNTER_INTS else None
 
 
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -413,21 +435,13 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     if splits > 1:
         part_o = torch.empty((S, heads, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((S, heads, splits, 2), dtype=torch.float32, device=q.device)
-    counters = None
-    if not scalar_kernel and splits > 1 and q.dtype == torch.bfloat16 and hd in (64, 128):
-        counters = _decode_counters(q.device, S * kvh * (-(-(heads // kvh) // 16)))
-    if scalar_kernel:
-        code = lib.ix_paged_attention_decode_scalar(
-            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
-            _ptr(part_ml), _ptr(out), _dtype_code(q), S, heads, kvh, hd, page,
-            block_table.shape[1], window, ctypes.c_float(scale), splits, _stream())
-    else:
-        code = lib.ix_paged_attention_decode_fused(
-            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
-            _ptr(part_ml), _ptr(counters), _ptr(out), _dtype_code(q), S, heads, kvh, hd, page,
-            block_table.shape[1], window, ctypes.c_float(scale), splits, _stream())
+    entry = lib.ix_paged_attention_decode_scalar if scalar_kernel else lib.ix_paged_attention_decode
+    code = entry(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
+        _ptr(part_ml), _ptr(out), _dtype_code(q), S, heads, kvh, hd, page, block_table.shape[1],
+        window, ctypes.c_float(scale), splits, _stream())
     _check(code, "paged_attention_decode")
-    _count(2 if (splits > 1 and counters is None) else 1)
+    _count(2 if splits > 1 else 1)
     return out
 
 

@@ -37,6 +37,9 @@ class Block:
     def forward(self, resid, pending, step: StepContext, cache: LayerCache):
         """``pending`` is the previous block's contribution not yet added to
         ``resid``; returns this block's own pending contribution."""
+        if hasattr(pending, "materialize") and not getattr(self.input_norm, "accepts_pending",
+                                                            False):
+            pending = pending.materialize()
         n = self.input_norm.forward(resid, pending)
         a = self.mixer.forward(n, step, cache)
         n = self.post_norm.forward(resid, a)
@@ -108,5 +111,8 @@ class DecoderModel:
             pending = self.blocks[entry.layer].forward(resid, pending, step, cache)
         if logit_rows is None or logit_rows.numel() == 0:
             return None
+        if hasattr(pending, "materialize") and not getattr(self.final_norm, "accepts_pending",
+                                                            False):
+            pending = pending.materialize()
         n = self.final_norm.forward(resid, pending, rows=logit_rows)
         return ops.linear(n, self.head, out_dtype=torch.float32)

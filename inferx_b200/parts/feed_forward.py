@@ -119,7 +119,8 @@ class MoeFeedForward:
             main.wait_stream(side)
         elif self.shared is not None:
             shared = self.shared.forward(x)
-        return ops.moe_combine(y, dest, topk_w, shared, shared_logit)
+        combine = getattr(ops, "moe_combine_pending", ops.moe_combine)
+        return combine(y, dest, topk_w, shared, shared_logit)
 
 
 register_part("feed_forward", "swiglu", SwiGluFeedForward)

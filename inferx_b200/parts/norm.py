@@ -13,6 +13,10 @@ from .registry import register_part
 
 
 class RmsNorm:
+    # the contribution to add may arrive unwritten (``ops.CombinePending``); the kernel
+    # behind ``add_rmsnorm`` folds it in
+    accepts_pending = True
+
     def __init__(self, spec, ctx, prefix: str):
         self.spec = spec
         self.ctx = ctx

@@ -99,6 +99,8 @@ def test_moe_part(dtype, renorm, shared, gated):
     for T in (4, 200):           # few tokens (streaming kernels) and many (tensor-core tiles)
         x = torch.randn(T, 64).to(dtype)
         out = part.forward(x.cuda())
+        if hasattr(out, "materialize"):      # the combine may be left to the next norm
+            out = out.materialize()
         ref = plain.moe_block(cfg, w, "mlp", x.float())
         _assert_close_scaled(out.float().cpu(), ref, dtype)
 
