@@ -389,6 +389,53 @@ def breakdown(rt, batch, context, steps, prefill_tokens=0):
     return "\n".join(lines)
 
 
+def serving(args):
+    """Continuous batching under memory pressure, in the shape of BASELINE.json's fifth
+    configuration: A2.7B layer sizes with every second layer dense, renormalised top-k
+    and a sliding window on the last three layers; requests with prompts of uniform random
+    length, a fixed number of decoded tokens each, prefill portions of 512 tokens beside
+    decoding sequences, and a cache pool sized to a fraction of what the requests would
+    need at once, so that sequences are preempted and recomputed.  Prints one JSON line
+    of its own (tokens per second, steps, preemptions)."""
+    import torch
+    from inferx_b200 import Engine, EngineConfig, Request, SamplingParams
+    layers = args.layers
+    cfg = dict(A27B, num_hidden_layers=layers, decoder_sparse_step=2, norm_topk_prob=True,
+               use_sliding_window=True, sliding_window=4096, max_window_layers=max(0, layers - 3))
+    n_req, max_prompt, new_tokens = args.requests, args.max_prompt, args.new_tokens
+    g = torch.Generator().manual_seed(5)
+    lens = torch.randint(16, max_prompt + 1, (n_req,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    page = 16
+    demand = sum(-(-(n + new_tokens) // page) for n in lens[:args.max_num_seqs])
+    longest = -(-(max_prompt + new_tokens) // page) + 1
+    pages = max(longest, int(args.pool_fraction * demand))
+    eng = Engine.create(EngineConfig(
+        config_json=cfg, dtype="bfloat16", max_num_seqs=args.max_num_seqs,
+        max_model_len=max_prompt + new_tokens + 8, max_num_batched_tokens=2048,
+        prefill_chunk=512, block_size=page, num_gpu_blocks_override=pages))
+    reqs = [Request(p, SamplingParams(max_tokens=new_tokens, ignore_eos=True)) for p in prompts]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = eng.generate(reqs)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    st = eng.stats()
+    reasons = {}
+    for c in outs:
+        reasons[c.reason] = reasons.get(c.reason, 0) + 1
+    print(json.dumps({
+        "workload": "serving", "requests": n_req, "max_num_seqs": args.max_num_seqs,
+        "prompt_tokens": sum(lens), "generated_tokens": st["tokens_generated"],
+        "seconds": round(dt, 3), "output_tok_s": round(st["tokens_generated"] / dt, 1),
+        "total_tok_s": round((st["tokens_generated"] + st["tokens_prefilled"]) / dt, 1),
+        "steps": st["steps"], "preemptions": st["preemptions"],
+        "tokens_prefilled_incl_recompute": st["tokens_prefilled"],
+        "pool_pages": pages, "pool_fraction_of_demand": args.pool_fraction,
+        "finish_reasons": reasons, "layers": layers, "layers_of_config": FULL_LAYERS}))
+    return 0
+
+
 def reference_arm():
     why = ("divedb/InferX is a C++20/CMake project with no Python package (no setup.py or "
            "pyproject.toml) and needs abseil, CLI11, folly and FlashInfer sources that are absent "
@@ -408,6 +455,13 @@ def main(argv=None):
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the default decode run")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--serving", action="store_true",
+                    help="continuous batching with preemption instead of the bench line")
+    ap.add_argument("--requests", type=int, default=64)
+    ap.add_argument("--max-num-seqs", type=int, default=16)
+    ap.add_argument("--max-prompt", type=int, default=6000)
+    ap.add_argument("--new-tokens", type=int, default=256)
+    ap.add_argument("--pool-fraction", type=float, default=0.6)
     ap.add_argument("--breakdown", choices=["decode", "prefill"],
                     help="print device time per kernel face instead of the bench line")
     args = ap.parse_args(argv)
@@ -421,6 +475,8 @@ def main(argv=None):
     import torch
     from inferx_b200.kernels import ops
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    if args.serving:
+        return serving(args)
     hbm_peak, tf_peak, peak_src = peaks()
     cfg = dict(A27B, num_hidden_layers=args.layers)
     B, C = args.batch, args.context
