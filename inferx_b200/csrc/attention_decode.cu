@@ -560,20 +560,28 @@ static int launch_decode_mma(const void* q, const void* kc, const void* vc, cons
   return ix_launch_status();
 }
 
-// The number of splits a caller should provide scratch for.
-IX_API int ix_attn_decode_splits(int S, int heads, int kvh, int max_kv_len) {
-  // One wave: three blocks fit on each of the 148 SMs, so aim for at most 444 blocks and
-  // let each of them walk a long range of keys; a grid a little larger than a wave
-  // would leave most SMs idle during its last wave.
+// One wave: with `per_sm` blocks resident on each of the 148 SMs, aim for at most
+// 148 * per_sm blocks and let each of them walk a long range of keys; a grid a little
+// larger than a wave would leave most SMs idle during its last wave.
+static int decode_splits(int S, int heads, int kvh, int max_kv_len, int per_sm) {
   const int rep = heads / (kvh > 0 ? kvh : 1);
   const long long base = (long long)S * kvh * ((rep + 15) / 16);
-  const int slots = 148 * 3;
+  const int slots = 148 * per_sm;
   long long splits = base >= slots ? 1 : slots / base;
   const int max_by_len = (max_kv_len + 127) / 128;   // at least two 64-key tiles per block
   if (splits > max_by_len) splits = max_by_len;
   if (splits > 64) splits = 64;
   if (splits < 1) splits = 1;
   return (int)splits;
+}
+
+// The number of splits a caller should provide scratch for: the cp.async-fed and
+// scalar kernels (three blocks per SM) and the TMA-fed kernel (two, with a deeper ring).
+IX_API int ix_attn_decode_splits(int S, int heads, int kvh, int max_kv_len) {
+  return decode_splits(S, heads, kvh, max_kv_len, 3);
+}
+IX_API int ix_attn_decode_tma_splits(int S, int heads, int kvh, int max_kv_len) {
+  return decode_splits(S, heads, kvh, max_kv_len, 2);
 }
 
 // variant 0: the tensor-core kernel where it applies (bf16, head_dim 64/128), else the
@@ -634,4 +642,37 @@ IX_API int ix_paged_attention_decode_scalar(const void* q, const void* k_cache,
                                             float scale, int splits, cudaStream_t stream) {
   return decode_dispatch(q, k_cache, v_cache, block_table, kv_len, part_o, part_ml, out, act_dtype,
                          S, heads, kvh, hd, page_size, max_blocks, window, scale, splits, 1, stream);
+}
+
+// The TMA-fed form (attention_decode_tma.cu) followed by the same merge.  bf16,
+// head_dim 64/128, page_size a power of two from 8 to 64; num_pages is the first
+// extent of the cache tensors.
+extern "C" int ix_attn_decode_tma_applies(int hd, int page_size);
+extern "C" int ix_attn_decode_tma_partials(const void* q, const void* kc, const void* vc,
+                                           int num_pages, const int* bt, const int* kv_len,
+                                           float* part_o, float* part_ml, void* out, int S,
+                                           int heads, int kvh, int hd, int page_size, int maxb,
+                                           int window, float scale, int splits, int* status,
+                                           cudaStream_t stream);
+
+IX_API int ix_paged_attention_decode_tma(const void* q, const void* k_cache, const void* v_cache,
+                                         int num_pages, const int* block_table,
+                                         const int* kv_len, float* part_o, float* part_ml,
+                                         void* out, int S, int heads, int kvh, int hd,
+                                         int page_size, int max_blocks, int window, float scale,
+                                         int splits, int* status, cudaStream_t stream) {
+  if (S <= 0) return IX_OK;
+  if (heads <= 0 || kvh <= 0 || heads % kvh != 0 || max_blocks <= 0 || window < 0 || splits < 1)
+    return IX_ERR_SIZE;
+  if (kvh * ((heads / kvh + 15) / 16) > 65535 || S > 65535) return IX_ERR_SIZE;
+  if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return IX_ERR_SIZE;
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return IX_ERR_ALIGN;
+  if (!ix_attn_decode_tma_applies(hd, page_size)) return IX_ERR_UNSUPPORTED;
+  int rc = ix_attn_decode_tma_partials(q, k_cache, v_cache, num_pages, block_table, kv_len, part_o,
+                                       part_ml, out, S, heads, kvh, hd, page_size, max_blocks,
+                                       window, scale, splits, status, stream);
+  if (rc != 0 || splits == 1) return rc;
+  ix_launch(attn_decode_merge_kernel<bf16, true>, dim3(S * heads), dim3(hd >= 128 ? 128 : 64), 0,
+            stream, (const float*)part_o, (const float*)part_ml, (bf16*)out, hd, splits);
+  return ix_launch_status();
 }

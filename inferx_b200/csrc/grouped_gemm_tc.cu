@@ -27,16 +27,14 @@
 //
 // Requires bf16, K a multiple of 8 (16-byte row pitch for TMA), 16-byte aligned
 // bases.  Anything else is refused with IX_ERR_UNSUPPORTED.
-#include <cuda.h>
-
 #include "common.cuh"
+#include "tma_common.cuh"
 
 #define TC_BM 128
 #define TC_BN 128
 #define TC_BK 64
 #define TC_THREADS 192
 #define TC_TILE_BYTES (TC_BM * TC_BK * 2)   // 16 KB: one 128 x 64 bf16 tile
-#define TC_WAIT_POLLS 4000000               // bounded waits: about a second at worst
 // two blocks per SM (96 KB of stages each), so that one block's epilogue and set-up
 // overlap the other's MMA work
 #define TC_STAGES_DUAL 2
@@ -47,53 +45,6 @@ enum { TC_ERR_PRODUCER = 1, TC_ERR_MMA = 2, TC_ERR_EPILOGUE = 3 };
 // ---------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ unsigned smem_u32(const void* p) {
-  return (unsigned)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false when the limit ran out or another role aborted.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity,
-                                          volatile int* abort_flag) {
-  for (int i = 0; i < TC_WAIT_POLLS; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (i > 1024) __nanosleep(64);
-  }
-  return false;
-}
-// Bounded wait that ignores the abort flag: used to let copies in flight land.
-__device__ __forceinline__ void mbar_drain(unsigned long long* bar, unsigned parity) {
-  for (int i = 0; i < TC_WAIT_POLLS / 16; ++i) {
-    if (mbar_try_wait(bar, parity)) return;
-    __nanosleep(64);
-  }
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
-                                            unsigned long long* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)),
-      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -329,38 +280,9 @@ IX_API int ix_gather_rows(const void* src, const int* rows, void* dst, int n_row
 }
 
 // ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
-            cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
 // 2-D bf16 tensor [rows, cols] with cols contiguous; boxes of 128 rows x 64 columns.
 static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return IX_ERR_UNSUPPORTED;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {TC_BK, TC_BM};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
-                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? IX_OK : IX_ERR_UNSUPPORTED;
+  return ix_tensor_map_bf16_2d(map, base, rows, cols, TC_BK, TC_BM);
 }
 
 // a: [A_rows, K] bf16 grouped rows; w: [E, (dual ? 2N : N), K] bf16; out: [A_rows, N] bf16.

@@ -184,6 +184,7 @@ class Engine:
                 done[c.id] = c
         for c in self.scheduler.take_completed():
             done[c.id] = c
+        self.runtime.executor.poll_errors()
         return [done[i] for i in ids]
 
     def stats(self) -> Dict[str, Any]:

@@ -276,7 +276,20 @@ class Executor:
         if fresh:
             self.storage.zero_slots(fresh)
         self.steps_run += 1
+        if self.steps_run % self.ERROR_POLL_STEPS == 0:
+            self.poll_errors()
         if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
             return self._graph_step(entries)
         ctx, rows, _ = self.build_context(entries)
         return self.model.forward(ctx, self.caches, rows)
+
+    # Kernels with bounded waits record a wait that ran out in a status word on the
+    # device instead of hanging; reading it synchronises, so it is read now and then
+    # (and by whoever ends a run) rather than every step.
+    ERROR_POLL_STEPS = 64
+
+    def poll_errors(self) -> None:
+        ops = getattr(getattr(self.model, "ctx", None), "ops", None)
+        check = getattr(ops, "check_async_errors", None)
+        if check is not None:
+            check()

@@ -84,6 +84,7 @@ def run_stream(session: ReplaySession, lines: Iterable[str], out_dir: str, repor
             arr.astype("<f4").tofile(os.path.join(out_dir, f"{step['step']}.f32"))
         elif session.executor.device.type == "cuda":
             torch.cuda.synchronize()
+        session.executor.poll_errors()
         if report is not None:
             report(step["step"])
         n += 1

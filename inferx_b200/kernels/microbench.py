@@ -79,12 +79,12 @@ def attn_decode(args):
 
     def fn(i):
         ops.paged_attention_decode(q, kcs[i], vcs[i], bt, kv_len, C, args.window, scale,
-                                   splits=args.splits or None)
+                                   splits=args.splits or None, kernel=args.form or None)
     us = _time(fn, n, args.iters)
     span = min(C, args.window) if args.window else C
     nbytes = B * span * kvh * hd * 2 * 2
     return {"case": "attn_decode", "batch": B, "context": C, "heads": heads, "kv_heads": kvh,
-            "head_dim": hd, "splits": args.splits, "us": round(us, 2), "bytes": nbytes,
+            "head_dim": hd, "splits": args.splits, "form": args.form or "auto", "us": round(us, 2), "bytes": nbytes,
             "GBps": round(nbytes / us / 1e3, 1)}
 
 
@@ -197,6 +197,7 @@ def main(argv=None):
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--form", default="", help="attn_decode: tma, mma or scalar (default: auto)")
     ap.add_argument("--hidden", type=int, default=2048)
     ap.add_argument("--inter", type=int, default=1408)
     ap.add_argument("--experts", type=int, default=60)

@@ -407,12 +407,23 @@ def append_kv(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: 
 _DECODE_HEAD_SIZES = {torch.bfloat16: (64, 128, 256), torch.float32: (64, 128)}
 
 
+# Decode attention forms: "tma" (keys and values brought in by TMA), "mma" (the same
+# arithmetic fed by cp.async), "scalar" (CUDA cores; fp32 and sizes the others refuse).
+USE_TMA_DECODE = True
+
+
+def _tma_decode_applies(q, page: int) -> bool:
+    return (q.dtype == torch.bfloat16 and q.shape[2] in (64, 128)
+            and page in (8, 16, 32, 64))
+
+
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                            block_table: torch.Tensor, kv_len: torch.Tensor, max_kv_len: int,
                            window: int, scale: float, splits: Optional[int] = None,
-                           scalar_kernel: bool = False):
+                           scalar_kernel: bool = False, kernel: Optional[str] = None):
     """Split-KV attention for a batch in which sequence s brings the one query q[s]
-    at position kv_len[s] - 1."""
+    at position kv_len[s] - 1.  ``kernel`` picks a form ("tma", "mma", "scalar");
+    None takes the fastest that applies."""
     _chk("q", q)
     _chk("k_cache", k_cache, q.dtype)
     _chk("v_cache", v_cache, q.dtype)
@@ -427,19 +438,40 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
                           "use the general kernel")
     if kv_len.numel() != S or block_table.shape[0] != S:
         raise KernelError("paged_attention_decode: one query per sequence is required")
+    if kernel is None:
+        if scalar_kernel:
+            kernel = "scalar"
+        elif USE_TMA_DECODE and _tma_decode_applies(q, page):
+            kernel = "tma"
+        else:
+            kernel = "mma"
+    if kernel not in ("tma", "mma", "scalar"):
+        raise KernelError(f"paged_attention_decode: no kernel form {kernel!r}")
+    if kernel == "tma" and not _tma_decode_applies(q, page):
+        raise KernelError(f"paged_attention_decode: the TMA form takes bf16, head size 64 or 128 "
+                          f"and a page of 8, 16, 32 or 64 keys (got {q.dtype}, {hd}, {page})")
     lib = _lib()
     if splits is None:
-        splits = lib.ix_attn_decode_splits(S, heads, kvh, int(max_kv_len))
+        pick = lib.ix_attn_decode_tma_splits if kernel == "tma" else lib.ix_attn_decode_splits
+        splits = pick(S, heads, kvh, int(max_kv_len))
     out = torch.empty_like(q)
     part_o = part_ml = None
     if splits > 1:
         part_o = torch.empty((S, heads, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((S, heads, splits, 2), dtype=torch.float32, device=q.device)
-    entry = lib.ix_paged_attention_decode_scalar if scalar_kernel else lib.ix_paged_attention_decode
-    code = entry(
-        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
-        _ptr(part_ml), _ptr(out), _dtype_code(q), S, heads, kvh, hd, page, block_table.shape[1],
-        window, ctypes.c_float(scale), splits, _stream())
+    if kernel == "tma":
+        code = lib.ix_paged_attention_decode_tma(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), P, _ptr(block_table), _ptr(kv_len),
+            _ptr(part_o), _ptr(part_ml), _ptr(out), S, heads, kvh, hd, page,
+            block_table.shape[1], window, ctypes.c_float(scale), splits,
+            _ptr(_tc_status(q.device)), _stream())
+    else:
+        entry = (lib.ix_paged_attention_decode_scalar if kernel == "scalar"
+                 else lib.ix_paged_attention_decode)
+        code = entry(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
+            _ptr(part_ml), _ptr(out), _dtype_code(q), S, heads, kvh, hd, page,
+            block_table.shape[1], window, ctypes.c_float(scale), splits, _stream())
     _check(code, "paged_attention_decode")
     _count(2 if splits > 1 else 1)
     return out
@@ -550,17 +582,25 @@ def _tc_status(device) -> torch.Tensor:
     return _TC_STATUS[key]
 
 
+_STATUS_ROLES = {
+    1: "grouped_gemm_tc: the TMA producer", 2: "grouped_gemm_tc: the MMA issuer",
+    3: "grouped_gemm_tc: the epilogue",
+    11: "paged_attention_decode (TMA form): the copying warp",
+    12: "paged_attention_decode (TMA form): a computing warp",
+}
+
+
 def check_async_errors():
-    """Raise if a tensor-core kernel gave up on one of its bounded waits.  Reads a
-    status word from the device, so it synchronises; call it where the host waits
-    for results anyway."""
+    """Raise if a kernel gave up on one of its bounded mbarrier waits.  Reads a status
+    word from the device, so it synchronises; call it where the host waits for
+    results anyway."""
     for key, st in _TC_STATUS.items():
         code = int(st.item())
         if code:
             st.zero_()
-            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, "?")
-            raise KernelError(f"grouped_gemm_tc on cuda:{key}: {role} waited past its limit "
-                              f"(status {code}); the output of that call is not valid")
+            role = _STATUS_ROLES.get(code, "a kernel")
+            raise KernelError(f"cuda:{key}: {role} waited past its limit (status {code}); "
+                              "the output of that call is not valid")
 
 
 def grouped_gemm_tc(a: torch.Tensor, offsets: torch.Tensor, w: torch.Tensor, dual: bool):

@@ -319,11 +319,23 @@ def test_cpu_tensor_is_refused():
         ops.linear(torch.zeros(2, 4).cuda(), torch.zeros(3, 4).cuda().to(torch.bfloat16))
 
 
+def _decode_forms(dtype, hd, page):
+    """The kernel forms that take this case: TMA-fed and cp.async-fed tensor-core
+    kernels (bf16, head size 64/128) and the scalar one."""
+    forms = ["scalar"]
+    if dtype == torch.bfloat16 and hd in (64, 128):
+        forms.append("mma")
+        if page in (8, 16, 32, 64):
+            forms.append("tma")
+    return forms
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kvh,hd,page,window,splits", [
     (4, 4, 128, 16, 0, None), (8, 2, 64, 8, 0, 3), (6, 3, 128, 16, 50, None),
     (16, 2, 64, 4, 0, 1), (3, 1, 128, 16, 7, 5), (2, 2, 256, 16, 0, None),
-    (40, 2, 64, 16, 0, 2), (5, 5, 128, 12, 0, None)])
+    (40, 2, 64, 16, 0, 2), (5, 5, 128, 12, 0, None), (6, 2, 128, 32, 0, 4),
+    (4, 1, 64, 64, 100, None), (7, 7, 128, 8, 130, 2), (34, 2, 128, 16, 0, 1)])
 def test_paged_attention_decode(dtype, heads, kvh, hd, page, window, splits):
     ops = _ops()
     if dtype == torch.float32 and hd == 256:
@@ -334,12 +346,34 @@ def test_paged_attention_decode(dtype, heads, kvh, hd, page, window, splits):
     kv_len = torch.tensor(seq_lens, dtype=torch.int32)
     scale = 1.0 / math.sqrt(hd)
     ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, window, scale)
+    if window > 0:
+        # pages that the window has wholly passed are given back: the table says -1 there
+        # and the page may hold anything
+        for s, n in enumerate(seq_lens):
+            for b in range(max(0, n - window) // page):
+                kc[bt[s, b]] = float("nan")
+                vc[bt[s, b]] = float("nan")
+                bt[s, b] = -1
     tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)
-    for scalar in (False, True):      # the tensor-core kernel (bf16, hd 64/128) and the scalar one
+    for form in _decode_forms(dtype, hd, page):
         out = ops.paged_attention_decode(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), kv_len.cuda(),
-                                         max(seq_lens), window, scale, splits=splits,
-                                         scalar_kernel=scalar)
-        torch.testing.assert_close(out.cpu().float(), ref.float(), **tol)
+                                         max(seq_lens), window, scale, splits=splits, kernel=form)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), **tol, msg=lambda m: f"{form}: {m}")
+    if hasattr(ops, "check_async_errors"):
+        ops.check_async_errors()
+
+
+def test_decode_attention_forms_refuse_what_they_do_not_take():
+    ops = _ops()
+    q, kc, vc, bt, _, _ = _paged_case(torch.bfloat16, 2, 2, 128, 12, 0, [20], [1])
+    with pytest.raises(ops.KernelError):
+        ops.paged_attention_decode(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(),
+                                   torch.tensor([20], dtype=torch.int32).cuda(), 20, 0, 1.0,
+                                   kernel="tma")
+    with pytest.raises(ops.KernelError):
+        ops.paged_attention_decode(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(),
+                                   torch.tensor([20], dtype=torch.int32).cuda(), 20, 0, 1.0,
+                                   kernel="other")
 
 
 def test_decode_attention_finds_one_far_key():
@@ -354,11 +388,13 @@ def test_decode_attention_finds_one_far_key():
         kc[bt[0, far // page], :, far % page] = key.to(torch.bfloat16)
         q[0, :, :] = (key * 2).to(torch.bfloat16)
         vc[bt[0, far // page], :, far % page, 0] = 1000.0
-        out = ops.paged_attention_decode(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(),
-                                         torch.tensor([n], dtype=torch.int32).cuda(), n, 0, 1.0)
         ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, 0, 1.0)
         assert ref[0, 0, 0] > 900
-        torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=1.0)
+        for form in ("tma", "mma", "scalar"):
+            out = ops.paged_attention_decode(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(),
+                                             torch.tensor([n], dtype=torch.int32).cuda(), n, 0,
+                                             1.0, kernel=form)
+            torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=1.0)
 
 
 @pytest.mark.parametrize("T,H,I,E,k", [(1, 64, 32, 4, 2), (9, 200, 72, 8, 3), (40, 96, 48, 60, 4),
