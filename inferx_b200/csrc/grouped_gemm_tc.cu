@@ -11,15 +11,29 @@
 // 647-705; src/backends/cuda/ops/layers.cu:512-529), whose own notes name a
 // tensor-core grouped GEMM as the upgrade (include/inferx/ops/moe.h:125-126).
 //
-// One block computes a 128 x 128 output tile of one expert (two accumulators when
-// DUAL: gate and up).  Warp 0 streams 128 x 64 tiles of A and W into a ring of
-// shared-memory stages with cp.async.bulk.tensor (128-byte swizzle); warp 1
-// issues tcgen05.mma (M 128, N 128, K 16 per instruction, bf16 in, fp32
-// accumulate in TMEM) and releases stages with tcgen05.commit; warps 2-5 read the
-// finished accumulator with tcgen05.ld, apply the epilogue and store bf16 rows
-// that belong to the expert.  Rows of the tile beyond the expert's range, columns
-// beyond N and the K tail are computed on whatever TMA delivered (neighbouring
-// rows or zero fill) and never stored.
+// The weights are the M side of the MMA and the tokens the N side.  An expert's row
+// count is ragged (a few hundred at most for a prompt portion of a few thousand
+// tokens) and M is fixed at 128 while N may be any multiple of 16 up to 256, so
+// this way round no tensor-core work is spent on padding, and - what matters more,
+// since at these sizes the product is bound by reading the experts' weights - each
+// 128-row tile of an expert's weights is read once for up to 256 of its tokens.
+//
+// The unit of work is, for one expert, 128 output features (gate and up rows when
+// DUAL: two accumulators) for a tile of up to BT (256 or 128) of the expert's tokens;
+// an expert with more rows is cut into equal tiles.
+// The kernel is persistent: one block per SM takes work items round robin, ordered so
+// that the feature tiles of one token tile run at the same time on neighbouring SMs
+// (they share the token rows through L2).  Warp 0 streams the tiles (weights 128 x
+// 64, tokens in boxes of 32 x 64) into a ring of shared-memory stages with
+// cp.async.bulk.tensor (128-byte swizzle) and runs ahead into the next work item;
+// warp 1 issues tcgen05.mma (M 128, N the tile's token count rounded up to 16, K 16
+// per instruction, bf16 in, fp32 accumulate in TMEM) and releases stages with
+// tcgen05.commit; warps 2-5 read the finished accumulator with tcgen05.ld (a thread
+// holds one feature for 32 tokens), apply the epilogue and store bf16.  Where tensor
+// memory has room for two accumulator sets, the epilogue of one item overlaps the MMAs
+// of the next.  Token rows of the last box beyond the tile, feature rows beyond N and
+// the K tail are computed on whatever TMA delivered (neighbouring rows or zero fill)
+// and never stored.
 //
 // Every wait on an mbarrier is bounded: after the limit the waiter records a code
 // in `status`, raises an abort flag that ends the other roles, and the block still
@@ -30,15 +44,13 @@
 #include "common.cuh"
 #include "tma_common.cuh"
 
-#define TC_BM 128
-#define TC_BN 128
+#define TC_BF 128        // output features per work item (the MMA's M)
+#define TC_BOX_T 32      // token rows per TMA box
 #define TC_BK 64
 #define TC_THREADS 192
-#define TC_TILE_BYTES (TC_BM * TC_BK * 2)   // 16 KB: one 128 x 64 bf16 tile
-// two blocks per SM (96 KB of stages each), so that one block's epilogue and set-up
-// overlap the other's MMA work
-#define TC_STAGES_DUAL 2
-#define TC_STAGES_PLAIN 3
+#define TC_W_BYTES (TC_BF * TC_BK * 2)   // 16 KB: one 128 x 64 bf16 weight tile
+#define TC_SMEM_STAGES (192 * 1024)      // shared memory given to the ring of stages
+#define TC_MAX_EXPERTS 1024              // the per-expert tile prefix lives in shared memory
 
 enum { TC_ERR_PRODUCER = 1, TC_ERR_MMA = 2, TC_ERR_EPILOGUE = 3 };
 
@@ -90,57 +102,105 @@ __device__ __forceinline__ unsigned long long umma_desc(const void* smem_tile) {
   return (unsigned long long)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) |
          (1ull << 46) | (2ull << 61);
 }
-// kind::f16, D fp32, A and B bf16, both K-major, N = 128, M = 128
-#define TC_IDESC ((1u << 4) | (1u << 7) | (1u << 10) | ((TC_BN >> 3) << 17) | ((TC_BM >> 4) << 24))
+// kind::f16, D fp32, A and B bf16, both K-major, M = 128, N = n (a multiple of 16)
+__device__ __forceinline__ unsigned tc_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) |
+         ((unsigned)(TC_BF >> 4) << 24);
+}
+
+// Tiles of an expert with `rows` rows: as few as hold BT each, of equal size (a
+// multiple of 16).
+template <int BT> __host__ __device__ __forceinline__ int tc_tiles_of(int rows) {
+  return (rows + BT - 1) / BT;
+}
+__device__ __forceinline__ int tc_tile_rows(int rows, int tiles) {
+  return ((rows + tiles - 1) / tiles + 15) & ~15;
+}
+
+struct TcItem {
+  int e, m0, n_valid, f0;
+};
+
+// Work item `w` of the launch: token tile w / f_tiles (found by bisection in the
+// prefix of tiles per expert), feature tile w % f_tiles.
+template <int BT>
+__device__ __forceinline__ TcItem tc_item(int w, int f_tiles, const int* tile_start,
+                                          const int* __restrict__ offsets, int E) {
+  const int tt = w / f_tiles;
+  int lo = 0, hi = E;                       // largest e with tile_start[e] <= tt
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tile_start[mid] <= tt) lo = mid; else hi = mid;
+  }
+  TcItem it;
+  it.e = lo;
+  const int r0 = offsets[lo], rows = offsets[lo + 1] - r0;
+  const int tiles_e = tc_tiles_of<BT>(rows);
+  const int per = tc_tile_rows(rows, tiles_e);
+  it.m0 = r0 + (tt - tile_start[lo]) * per;
+  it.n_valid = max(0, min(r0 + rows - it.m0, per));
+  it.f0 = (w - tt * f_tiles) * TC_BF;
+  return it;
+}
 
 // ---------------------------------------------------------------------------
-template <bool DUAL>
-__global__ void __launch_bounds__(TC_THREADS)
+template <bool DUAL, int BT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_w,
                        const int* __restrict__ offsets, bf16* __restrict__ out, int N, int K,
                        int E, int w_rows_per_expert, int* __restrict__ status) {
-  constexpr int STAGES = DUAL ? TC_STAGES_DUAL : TC_STAGES_PLAIN;
-  constexpr int STAGE_BYTES = TC_TILE_BYTES * (DUAL ? 3 : 2);
-  constexpr unsigned TMEM_COLS = DUAL ? 256 : 128;
+  constexpr int A_BYTES = BT * TC_BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + TC_W_BYTES * (DUAL ? 2 : 1);
+  constexpr int STAGES = TC_SMEM_STAGES / STAGE_BYTES;
+  constexpr int ACC_COLS = BT * (DUAL ? 2 : 1);          // one accumulator set
+  constexpr int NBUF = ACC_COLS * 2 <= 512 ? 2 : 1;
+  constexpr unsigned TMEM_COLS = ACC_COLS * NBUF;
+  static_assert(STAGES >= 2 && STAGES <= 8, "ring depth");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles =
       reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) unsigned long long full_bar[STAGES];
   __shared__ __align__(8) unsigned long long empty_bar[STAGES];
-  __shared__ __align__(8) unsigned long long accum_bar;
+  __shared__ __align__(8) unsigned long long acc_full[NBUF];
+  __shared__ __align__(8) unsigned long long acc_empty[NBUF];
   __shared__ unsigned tmem_holder;
   __shared__ int abort_flag;
+  __shared__ int tile_start[TC_MAX_EXPERTS + 1];
 
-  // which expert and which 128-row tile of it
-  int e = 0, m0 = 0, m_end = 0;
-  {
-    int tile = blockIdx.y;
-    bool found = false;
-    for (int ee = 0; ee < E; ++ee) {
-      const int lo = offsets[ee], hi = offsets[ee + 1];
-      const int tiles_e = (hi - lo + TC_BM - 1) / TC_BM;
-      if (tile < tiles_e) {
-        e = ee; m0 = lo + tile * TC_BM; m_end = hi; found = true;
-        break;
-      }
-      tile -= tiles_e;
-    }
-    if (!found) return;   // before any barrier or allocation: the whole block leaves
-  }
-  const int n0 = blockIdx.x * TC_BN;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_tiles = (K + TC_BK - 1) / TC_BK;
+  const int f_tiles = (N + TC_BF - 1) / TC_BF;
 
+  // prefix of token tiles per expert (warp 2, 32 experts at a time)
+  if (warp == 2) {
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int t = e < E ? tc_tiles_of<BT>(offsets[e + 1] - offsets[e]) : 0;
+      int incl = t;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      if (e < E) tile_start[e] = carry + incl - t;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) tile_start[E] = carry;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&accum_bar, 1);
+    for (int b = 0; b < NBUF; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);          // one arrival per epilogue warp
+    }
     abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_init_fence();
+    fence_proxy_async();
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -154,99 +214,116 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_after();
   const unsigned tmem_base = tmem_holder;
   volatile int* abortp = &abort_flag;
+  const int n_items = tile_start[E] * f_tiles;
 
   if (warp == 0) {
     if (lane == 0) {
-      int armed = 0;
+      int fill = 0;            // k-tiles issued so far, over all items
       bool ok = true;
-      for (int kt = 0; kt < k_tiles && ok; ++kt) {
-        const int s = kt % STAGES;
-        ok = mbar_wait(&empty_bar[s], ((kt / STAGES) & 1) ^ 1, abortp);
-        if (!ok) break;
-        unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-        tma_load_2d(st, &map_a, kt * TC_BK, m0, &full_bar[s]);
-        tma_load_2d(st + TC_TILE_BYTES, &map_w, kt * TC_BK, e * w_rows_per_expert + n0,
-                    &full_bar[s]);
-        if (DUAL)
-          tma_load_2d(st + 2 * TC_TILE_BYTES, &map_w, kt * TC_BK,
-                      e * w_rows_per_expert + N + n0, &full_bar[s]);
-        armed = kt + 1;
+      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+        const TcItem it = tc_item<BT>(w, f_tiles, tile_start, offsets, E);
+        if (it.n_valid <= 0) continue;
+        const int boxes = (((it.n_valid + 15) & ~15) + TC_BOX_T - 1) / TC_BOX_T;
+        const unsigned stage_tx =
+            (unsigned)(TC_W_BYTES * (DUAL ? 2 : 1) + boxes * TC_BOX_T * TC_BK * 2);
+        for (int kt = 0; kt < k_tiles; ++kt, ++fill) {
+          const int s = fill % STAGES;
+          ok = mbar_wait(&empty_bar[s], ((fill / STAGES) & 1) ^ 1, abortp);
+          if (!ok) break;
+          unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], stage_tx);
+          tma_load_2d(st + A_BYTES, &map_w, kt * TC_BK, it.e * w_rows_per_expert + it.f0,
+                      &full_bar[s]);
+          if (DUAL)
+            tma_load_2d(st + A_BYTES + TC_W_BYTES, &map_w, kt * TC_BK,
+                        it.e * w_rows_per_expert + N + it.f0, &full_bar[s]);
+          for (int b = 0; b < boxes; ++b)
+            tma_load_2d(st + b * (TC_BOX_T * TC_BK * 2), &map_a, kt * TC_BK,
+                        it.m0 + b * TC_BOX_T, &full_bar[s]);
+        }
       }
       if (!ok) {
         if (!*abortp) { atomicExch(status, TC_ERR_PRODUCER); *abortp = 1; }
         // let copies already issued land before the block's shared memory goes away
-        for (int kt = max(0, armed - STAGES); kt < armed; ++kt)
-          mbar_drain(&full_bar[kt % STAGES], (kt / STAGES) & 1);
+        for (int f = max(0, fill - STAGES); f < fill; ++f)
+          mbar_drain(&full_bar[f % STAGES], (f / STAGES) & 1);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      int drain = 0, n_done = 0;
       bool ok = true;
-      for (int kt = 0; kt < k_tiles && ok; ++kt) {
-        const int s = kt % STAGES;
-        ok = mbar_wait(&full_bar[s], (kt / STAGES) & 1, abortp);
+      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+        const TcItem it = tc_item<BT>(w, f_tiles, tile_start, offsets, E);
+        if (it.n_valid <= 0) continue;
+        const unsigned idesc = tc_idesc((it.n_valid + 15) & ~15);
+        const int buf = n_done % NBUF;
+        // the epilogue must have read this accumulator set's previous contents
+        ok = mbar_wait(&acc_empty[buf], ((n_done / NBUF) & 1) ^ 1, abortp);
         if (!ok) break;
         tc_fence_after();
-        unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
-        const unsigned long long ad = umma_desc(st);
-        const unsigned long long bd = umma_desc(st + TC_TILE_BYTES);
-        const unsigned long long ud = umma_desc(st + 2 * TC_TILE_BYTES);
+        const unsigned acc = tmem_base + buf * ACC_COLS;
+        for (int kt = 0; kt < k_tiles; ++kt, ++drain) {
+          const int s = drain % STAGES;
+          ok = mbar_wait(&full_bar[s], (drain / STAGES) & 1, abortp);
+          if (!ok) break;
+          tc_fence_after();
+          unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+          const unsigned long long td = umma_desc(st);                          // tokens: N side
+          const unsigned long long gd = umma_desc(st + A_BYTES);                // weights: M side
+          const unsigned long long ud = umma_desc(st + A_BYTES + TC_W_BYTES);
 #pragma unroll
-        for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
-          const unsigned accum = (kt > 0 || k4 > 0) ? 1u : 0u;
-          // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
-          tc_mma(tmem_base, ad + 2 * k4, bd + 2 * k4, TC_IDESC, accum);
-          if (DUAL) tc_mma(tmem_base + TC_BN, ad + 2 * k4, ud + 2 * k4, TC_IDESC, accum);
+          for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
+            const unsigned accum = (kt > 0 || k4 > 0) ? 1u : 0u;
+            // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
+            tc_mma(acc, gd + 2 * k4, td + 2 * k4, idesc, accum);
+            if (DUAL) tc_mma(acc + BT, ud + 2 * k4, td + 2 * k4, idesc, accum);
+          }
+          tc_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
         }
-        tc_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
+        if (!ok) break;
+        tc_commit(&acc_full[buf]);
+        ++n_done;
       }
-      if (ok) tc_commit(&accum_bar);
-      else if (!*abortp) { atomicExch(status, TC_ERR_MMA); *abortp = 1; }
+      if (!ok && !*abortp) { atomicExch(status, TC_ERR_MMA); *abortp = 1; }
     }
   } else {
-    const bool ok = mbar_wait(&accum_bar, 0, abortp);
-    if (!ok) {
-      if (lane == 0 && !*abortp) { atomicExch(status, TC_ERR_EPILOGUE); *abortp = 1; }
-    } else {
+    const int quarter = warp & 3;              // TMEM lanes this warp may read
+    int n_done = 0;
+    for (int w = blockIdx.x; w < n_items; w += gridDim.x) {
+      const TcItem it = tc_item<BT>(w, f_tiles, tile_start, offsets, E);
+      if (it.n_valid <= 0) continue;
+      const int buf = n_done % NBUF;
+      if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (n_done / NBUF) & 1, abortp))) {
+        if (lane == 0 && !*abortp) { atomicExch(status, TC_ERR_EPILOGUE); *abortp = 1; }
+        break;
+      }
       tc_fence_after();
-      const int quarter = warp & 3;              // TMEM lanes this warp may read
-      const int row = quarter * 32 + lane;
-      const int r = m0 + row;
-      const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16);
-      for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+      const int f = it.f0 + quarter * 32 + lane;    // this thread's output feature
+      const bool f_ok = f < N;
+      const unsigned taddr = tmem_base + buf * ACC_COLS + ((unsigned)(quarter * 32) << 16);
+      for (int c0 = 0; c0 < it.n_valid; c0 += 32) {
         float g[32], u[DUAL ? 32 : 1];
         tc_ld32(taddr + c0, g);
-        if (DUAL) tc_ld32(taddr + TC_BN + c0, u);
-        if (r < m_end) {
-          bf16* dst = out + (size_t)r * N + n0 + c0;
-          if (n0 + c0 + 32 <= N && (N % 8) == 0) {
+        if (DUAL) tc_ld32(taddr + BT + c0, u);
+        if (c0 + 32 >= it.n_valid) {
+          // everything this warp needs is in registers: hand the accumulator back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+        // a warp's 32 threads hold 32 neighbouring features of one token: 64-byte stores
+        bf16* dst = out + (size_t)(it.m0 + c0) * N + f;
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              unsigned pk[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float a = g[i + 2 * j], b = g[i + 2 * j + 1];
-                if (DUAL) {
-                  a = a / (1.0f + __expf(-a)) * u[i + 2 * j];
-                  b = b / (1.0f + __expf(-b)) * u[i + 2 * j + 1];
-                }
-                __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-                pk[j] = *reinterpret_cast<unsigned*>(&v);
-              }
-              *reinterpret_cast<uint4*>(dst + i) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            }
-          } else {
-            for (int i = 0; i < 32; ++i) {
-              if (n0 + c0 + i < N) {
-                float a = g[i];
-                if (DUAL) a = a / (1.0f + __expf(-a)) * u[i];
-                dst[i] = __float2bfloat16_rn(a);
-              }
-            }
+        for (int i = 0; i < 32; ++i) {
+          if (f_ok && c0 + i < it.n_valid) {
+            float a = g[i];
+            if (DUAL) a = a / (1.0f + __expf(-a)) * u[i];
+            dst[(size_t)i * N] = __float2bfloat16_rn(a);
           }
         }
       }
+      ++n_done;
     }
   }
   tc_fence_before();
@@ -280,45 +357,55 @@ IX_API int ix_gather_rows(const void* src, const int* rows, void* dst, int n_row
 }
 
 // ---------------------------------------------------------------------------
-// 2-D bf16 tensor [rows, cols] with cols contiguous; boxes of 128 rows x 64 columns.
-static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols) {
-  return ix_tensor_map_bf16_2d(map, base, rows, cols, TC_BK, TC_BM);
-}
-
 // a: [A_rows, K] bf16 grouped rows; w: [E, (dual ? 2N : N), K] bf16; out: [A_rows, N] bf16.
 // status: one int in device memory, zero before the first call; a bounded wait that
 // ran out leaves a nonzero code there.
+template <bool DUAL, int BT>
+static int launch_tc(const void* a, const int* offsets, const void* w, void* out, int A_rows,
+                     int N, int K, int E, long long w_rows, int* status, cudaStream_t stream) {
+  CUtensorMap map_a, map_w;
+  int rc = ix_tensor_map_bf16_2d(&map_a, a, A_rows, K, TC_BK, TC_BOX_T);
+  if (rc != IX_OK) return rc;
+  rc = ix_tensor_map_bf16_2d(&map_w, w, (long long)E * w_rows, K, TC_BK, TC_BF);
+  if (rc != IX_OK) return rc;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        sms <= 0)
+      sms = 148;
+  }
+  // every expert can add a partial token tile
+  const long long items =
+      ((long long)tc_tiles_of<BT>(A_rows) + E) * ((N + TC_BF - 1) / TC_BF);
+  const int grid = (int)(items < sms ? items : sms);
+  const int smem = TC_SMEM_STAGES + 1024;
+  auto kern = grouped_gemm_tc_kernel<DUAL, BT>;
+  cudaError_t e2 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e2 != cudaSuccess) return (int)e2;
+  kern<<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, offsets, (bf16*)out, N, K, E,
+                                           (int)w_rows, status);
+  return ix_launch_status();
+}
+
 IX_API int ix_grouped_gemm_tc(const void* a, const int* offsets, const void* w, void* out,
                               int dual, int A_rows, int N, int K, int E, int* status,
                               cudaStream_t stream) {
   if (A_rows <= 0) return IX_OK;
   if (N <= 0 || K <= 0 || E <= 0 || status == nullptr) return IX_ERR_SIZE;
-  if (K % 8 != 0) return IX_ERR_UNSUPPORTED;
+  if (K % 8 != 0 || E > TC_MAX_EXPERTS) return IX_ERR_UNSUPPORTED;
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) & 15) return IX_ERR_ALIGN;
   const long long w_rows = dual ? 2LL * N : N;
   if ((long long)E * w_rows > 0x7fffffffLL) return IX_ERR_SIZE;
-  CUtensorMap map_a, map_w;
-  int rc = make_map(&map_a, a, A_rows, K);
-  if (rc != IX_OK) return rc;
-  rc = make_map(&map_w, w, (long long)E * w_rows, K);
-  if (rc != IX_OK) return rc;
-  const int m_tiles = (A_rows + TC_BM - 1) / TC_BM + E;   // every expert can add a partial tile
-  if (m_tiles > 65535) return IX_ERR_SIZE;
-  dim3 grid((N + TC_BN - 1) / TC_BN, m_tiles);
-  if (dual) {
-    const int smem = TC_STAGES_DUAL * TC_TILE_BYTES * 3 + 1024;
-    auto kern = grouped_gemm_tc_kernel<true>;
-    cudaError_t e2 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e2 != cudaSuccess) return (int)e2;
-    kern<<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, offsets, (bf16*)out, N, K, E,
-                                             (int)w_rows, status);
-  } else {
-    const int smem = TC_STAGES_PLAIN * TC_TILE_BYTES * 2 + 1024;
-    auto kern = grouped_gemm_tc_kernel<false>;
-    cudaError_t e2 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e2 != cudaSuccess) return (int)e2;
-    kern<<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, offsets, (bf16*)out, N, K, E,
-                                             (int)w_rows, status);
-  }
-  return ix_launch_status();
+  // SwiGLU form: 128-token tiles always, since two accumulator sets of that width fit
+  // in tensor memory and the epilogue (exp, divide) of one item then overlaps the next
+  // item's MMAs; with 256-token tiles it could not, and that cost more than reading the
+  // weights a second time out of L2.  Plain form: 256-token tiles (each weight tile
+  // read once) unless experts have so few rows that the narrow tile's deeper ring wins.
+  if (dual)
+    return launch_tc<true, 128>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream);
+  if (A_rows / E <= 96)
+    return launch_tc<false, 128>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream);
+  return launch_tc<false, 256>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream);
 }

@@ -149,6 +149,7 @@ __device__ __forceinline__ void dot8(float& acc, const float* xf, const float4& 
 }
 
 #define ROUTER_VTHREADS 512
+#define ROUTER_VROWS 4
 
 template <int ROUTER_VTOK>
 __global__ void __launch_bounds__(ROUTER_VTHREADS)
@@ -170,44 +171,47 @@ router_topk_bf16_vec_kernel(const bf16* __restrict__ x, const float* __restrict_
   }
   __syncthreads();
   const int rows_total = E + (extra_w ? 1 : 0);
-  for (int e = warp; e < rows_total; e += nwarps) {
-    const float4* wr = reinterpret_cast<const float4*>(e < E ? w + (size_t)e * H : extra_w);
-    float acc[ROUTER_VTOK];
+  // A warp takes ROUTER_VROWS weight rows at a time, so that a chunk of activations
+  // read from shared memory and widened once feeds that many dot products (one row at
+  // a time the loop is bound by shared-memory reads, not by the multiply-adds).
+  for (int e0 = warp * ROUTER_VROWS; e0 < rows_total; e0 += nwarps * ROUTER_VROWS) {
+    const float4* wr[ROUTER_VROWS];
 #pragma unroll
-    for (int tk = 0; tk < ROUTER_VTOK; ++tk) acc[tk] = 0.f;
-    // four chunks of weights are fetched before they are used, so that their latency
-    // overlaps the arithmetic of the previous four
-    for (int c0 = lane; c0 < chunks; c0 += 32 * 4) {
-      float4 wa[4], wb[4];
+    for (int r = 0; r < ROUTER_VROWS; ++r) {
+      const int e = min(e0 + r, rows_total - 1);       // a row past the end repeats the last
+      wr[r] = reinterpret_cast<const float4*>(e < E ? w + (size_t)e * H : extra_w);
+    }
+    float acc[ROUTER_VTOK][ROUTER_VROWS];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = c0 + u * 32;
-        if (c < chunks) {
-          wa[u] = wr[2 * c];
-          wb[u] = wr[2 * c + 1];
-        }
+    for (int tk = 0; tk < ROUTER_VTOK; ++tk)
+#pragma unroll
+      for (int r = 0; r < ROUTER_VROWS; ++r) acc[tk][r] = 0.f;
+    for (int c = lane; c < chunks; c += 32) {
+      float4 wa[ROUTER_VROWS], wb[ROUTER_VROWS];
+#pragma unroll
+      for (int r = 0; r < ROUTER_VROWS; ++r) {
+        wa[r] = wr[r][2 * c];
+        wb[r] = wr[r][2 * c + 1];
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = c0 + u * 32;
-        if (c < chunks) {
+      for (int tk = 0; tk < ROUTER_VTOK; ++tk) {
+        float xf[8];
+        bf8_to_f32(xs[tk * chunks + c], xf);
 #pragma unroll
-          for (int tk = 0; tk < ROUTER_VTOK; ++tk) {
-            float xf[8];
-            bf8_to_f32(xs[tk * chunks + c], xf);
-            dot8(acc[tk], xf, wa[u], wb[u]);
-          }
-        }
+        for (int r = 0; r < ROUTER_VROWS; ++r) dot8(acc[tk][r], xf, wa[r], wb[r]);
       }
     }
 #pragma unroll
-    for (int tk = 0; tk < ROUTER_VTOK; ++tk) {
-      const float v = warp_sum(acc[tk]);
-      if (lane == 0) {
-        if (e < E) lg[tk * E + e] = v;
-        else if (t0 + tk < T) extra_out[t0 + tk] = v;
+    for (int tk = 0; tk < ROUTER_VTOK; ++tk)
+#pragma unroll
+      for (int r = 0; r < ROUTER_VROWS; ++r) {
+        const float v = warp_sum(acc[tk][r]);
+        const int e = e0 + r;
+        if (lane == 0 && e < rows_total) {
+          if (e < E) lg[tk * E + e] = v;
+          else if (t0 + tk < T) extra_out[t0 + tk] = v;
+        }
       }
-    }
   }
   __syncthreads();
   for (int tk = warp; tk < ROUTER_VTOK; tk += nwarps) {

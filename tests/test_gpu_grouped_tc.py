@@ -18,9 +18,10 @@ def _routing(T, E, k, seed):
 
 
 @pytest.mark.parametrize("T,H,I,E,k", [
-    (300, 256, 192, 5, 2),      # partial tiles in M and N
+    (300, 256, 192, 5, 2),      # partial tiles of tokens and of features
     (70, 200, 104, 3, 2),       # K tails (200 = 3*64 + 8, 104 = 64 + 40)
-    (1000, 128, 128, 4, 1),     # several full M tiles per expert
+    (1000, 128, 128, 4, 1),     # about 250 rows per expert: one wide tile each
+    (2000, 128, 136, 3, 1),     # several token tiles per expert
     (64, 2048, 1408, 6, 4),     # the bench's widths
 ])
 def test_grouped_gemm_tc(T, H, I, E, k):
@@ -48,21 +49,22 @@ def test_grouped_gemm_tc_empty_experts_and_one_hot_rows():
     from inferx_b200.kernels import ops
     E, N, K = 4, 128, 128
     w = _rand((E, N, K), 1.0, 7)
-    rows_per = [0, 130, 0, 3]
-    A = sum(rows_per)
-    a = torch.zeros(A, K, dtype=torch.bfloat16)
-    for r in range(A):
-        a[r, (r * 7) % K] = 1.0
-    off = torch.tensor([0, 0, 130, 130, 133], dtype=torch.int32)
-    out = ops.grouped_gemm_tc(a.cuda(), off.cuda(), w.cuda(), False)
-    ops.check_async_errors()
-    ref = host_ops.grouped_down(a, off, w)
-    assert torch.equal(out.cpu(), ref)
+    for rows_per in ([0, 130, 0, 3], [257, 0, 700, 16], [1, 1, 1, 1]):
+        A = sum(rows_per)
+        a = torch.zeros(A, K, dtype=torch.bfloat16)
+        for r in range(A):
+            a[r, (r * 7) % K] = 1.0
+        off = torch.tensor([0] + list(torch.tensor(rows_per).cumsum(0)), dtype=torch.int32)
+        out = ops.grouped_gemm_tc(a.cuda(), off.cuda(), w.cuda(), False)
+        ops.check_async_errors()
+        ref = host_ops.grouped_down(a, off, w)
+        assert torch.equal(out.cpu(), ref), rows_per
 
 
 def test_grouped_gemm_tc_odd_width_and_refusal():
-    """N that is no multiple of 8 takes the scalar store path; K that is no multiple
-    of 8 cannot be described to TMA and is refused, never computed wrongly."""
+    """A feature count that is no multiple of the tile (or of 8) is masked at the
+    store; K that is no multiple of 8 cannot be described to TMA and is refused, never
+    computed wrongly."""
     from inferx_b200.kernels import ops
     E, N, K = 3, 100, 72
     w = _rand((E, N, K), 0.3, 9)
