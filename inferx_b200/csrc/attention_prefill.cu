@@ -85,7 +85,10 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
   unsigned char* Vs = Ks + 2 * PF_BN * HD * 2;            // [2][BN][HD]
 
   // which sequence and which 64-query tile of it
-  int s = 0, tile = blockIdx.x;
+  // blocks are handed out in launch order; the tiles with the most keys to walk (the
+  // last queries of a sequence) come first, all heads of a tile together, so that the
+  // short tiles fill the end of the grid
+  int s = 0, tile = gridDim.y - 1 - blockIdx.y;
   {
     bool found = false;
     for (int ss = 0; ss < S; ++ss) {
@@ -96,7 +99,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
     }
     if (!found) return;
   }
-  const int h = blockIdx.y;
+  const int h = blockIdx.x;
   const int kh = h / (heads / kvh);
   const int tok0 = cu_q[s];
   const int nq = cu_q[s + 1] - tok0;
@@ -284,8 +287,8 @@ static int launch_prefill(const void* q, const void* kc, const void* vc, const i
     if (e != cudaSuccess) return (int)e;
   }
   const int tiles = (T + PF_BM - 1) / PF_BM + S;   // every sequence can add one partial tile
-  if (heads > 65535) return IX_ERR_SIZE;
-  dim3 grid(tiles, heads);
+  if (tiles > 65535) return IX_ERR_SIZE;
+  dim3 grid(heads, tiles);
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}

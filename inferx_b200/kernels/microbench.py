@@ -177,10 +177,12 @@ def attn_prefill(args):
     scale = 1.0 / math.sqrt(hd)
 
     def fn(i):
-        ops.paged_attention(q, kc, vc, bt, step, args.window, scale)
+        ops.paged_attention_prefill(q, kc, vc, bt, step.cu_q, step.q_pos0, args.window, scale,
+                                    kernel=args.form or None)
     us = _time(fn, 1, args.iters)
     flops = 4 * heads * hd * T * T / 2
     return {"case": "attn_prefill", "tokens": T, "heads": heads, "head_dim": hd,
+            "form": args.form or "auto",
             "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
@@ -197,7 +199,7 @@ def main(argv=None):
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--splits", type=int, default=0)
-    ap.add_argument("--form", default="", help="attn_decode: tma, mma or scalar (default: auto)")
+    ap.add_argument("--form", default="", help="attn_decode: tma, mma or scalar; attn_prefill: tc or mma (default: auto)")
     ap.add_argument("--hidden", type=int, default=2048)
     ap.add_argument("--inter", type=int, default=1408)
     ap.add_argument("--experts", type=int, default=60)

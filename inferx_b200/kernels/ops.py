@@ -480,11 +480,22 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
 _PREFILL_HEAD_SIZES = {torch.bfloat16: (64, 128)}
 
 
+# Prompt attention forms: "tc" (tcgen05, S and O in tensor memory, K/V by TMA) and
+# "mma" (mma.sync tiles fed by cp.async; any page size).
+USE_TCGEN05_ATTENTION = True
+
+
+def _tc_prefill_applies(q, page: int) -> bool:
+    return (q.dtype == torch.bfloat16 and q.shape[2] in (64, 128)
+            and page in (8, 16, 32, 64))
+
+
 def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                             block_table: torch.Tensor, cu_q: torch.Tensor, q_pos0: torch.Tensor,
-                            window: int, scale: float):
+                            window: int, scale: float, kernel: Optional[str] = None):
     """Tensor-core attention for a ragged batch: sequence s brings the queries
-    q[cu_q[s]:cu_q[s+1]] at positions q_pos0[s], q_pos0[s]+1, ..."""
+    q[cu_q[s]:cu_q[s+1]] at positions q_pos0[s], q_pos0[s]+1, ...  ``kernel`` picks a
+    form ("tc", "mma"); None takes the fastest that applies."""
     _chk("q", q, torch.bfloat16)
     _chk("k_cache", k_cache, q.dtype)
     _chk("v_cache", v_cache, q.dtype)
@@ -501,11 +512,25 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                           "general kernel")
     if cu_q.numel() != S + 1 or block_table.shape[0] != S:
         raise KernelError("paged_attention_prefill: cu_q, q_pos0 and block_table disagree")
+    if kernel is None:
+        kernel = "tc" if USE_TCGEN05_ATTENTION and _tc_prefill_applies(q, page) else "mma"
+    if kernel not in ("tc", "mma"):
+        raise KernelError(f"paged_attention_prefill: no kernel form {kernel!r}")
+    if kernel == "tc" and not _tc_prefill_applies(q, page):
+        raise KernelError(f"paged_attention_prefill: the tcgen05 form takes bf16, head size 64 "
+                          f"or 128 and a page of 8, 16, 32 or 64 keys (got {q.dtype}, {hd}, "
+                          f"{page})")
     out = torch.empty_like(q)
-    code = _lib().ix_paged_attention_prefill(
-        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(cu_q), _ptr(q_pos0),
-        _ptr(out), _dtype_code(q), T, S, heads, kvh, hd, page, block_table.shape[1], window,
-        ctypes.c_float(scale), _stream())
+    if kernel == "tc":
+        code = _lib().ix_paged_attention_prefill_tc(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), P, _ptr(block_table), _ptr(cu_q),
+            _ptr(q_pos0), _ptr(out), T, S, heads, kvh, hd, page, block_table.shape[1], window,
+            ctypes.c_float(scale), _ptr(_tc_status(q.device)), _stream())
+    else:
+        code = _lib().ix_paged_attention_prefill(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(cu_q), _ptr(q_pos0),
+            _ptr(out), _dtype_code(q), T, S, heads, kvh, hd, page, block_table.shape[1], window,
+            ctypes.c_float(scale), _stream())
     _check(code, "paged_attention_prefill")
     _count()
     return out
@@ -587,6 +612,10 @@ _STATUS_ROLES = {
     3: "grouped_gemm_tc: the epilogue",
     11: "paged_attention_decode (TMA form): the copying warp",
     12: "paged_attention_decode (TMA form): a computing warp",
+    21: "paged_attention_prefill (tcgen05 form): the copying warp",
+    22: "paged_attention_prefill (tcgen05 form): the MMA issuer",
+    23: "paged_attention_prefill (tcgen05 form): a softmax warp",
+    24: "paged_attention_prefill (tcgen05 form): shared memory not on a 1024-byte mark;",
 }
 
 

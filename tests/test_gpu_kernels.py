@@ -457,14 +457,19 @@ def test_router_paths_agree_bitwise():
     assert torch.equal(ti[:40], ti2) and torch.equal(tw[:40], tw2) and torch.equal(ex[:40], ex2)
 
 
+def _prefill_forms(page):
+    """The mma.sync form takes any page size, the tcgen05 form powers of two from 8 to 64."""
+    return ["mma", "tc"] if page in (8, 16, 32, 64) else ["mma"]
+
+
 @pytest.mark.parametrize("heads,kvh,hd,page,window", [
     (4, 2, 128, 16, 0), (3, 1, 64, 8, 0), (2, 2, 128, 4, 40), (6, 3, 64, 16, 7),
-    (2, 1, 128, 16, 100)])
+    (2, 1, 128, 16, 100), (5, 5, 128, 32, 0), (2, 1, 64, 64, 260), (3, 3, 128, 8, 33)])
 def test_paged_attention_prefill(heads, kvh, hd, page, window):
     """Ragged batch: whole prompts, a portion deep in a sequence, single tokens."""
     ops = _ops()
     dtype = torch.bfloat16
-    seq_lens, q_lens = [150, 1, 333, 64, 65, 700], [150, 1, 70, 64, 2, 1]
+    seq_lens, q_lens = [150, 1, 333, 64, 65, 700, 520], [150, 1, 70, 64, 2, 1, 390]
     q, kc, vc, bt, seq_of, pos = _paged_case(dtype, heads, kvh, hd, page, window, seq_lens, q_lens,
                                              seed=hd + window)
     cu = [0]
@@ -473,10 +478,43 @@ def test_paged_attention_prefill(heads, kvh, hd, page, window):
     cu_q = torch.tensor(cu, dtype=torch.int32)
     q_pos0 = torch.tensor([n - ql for n, ql in zip(seq_lens, q_lens)], dtype=torch.int32)
     scale = 1.0 / math.sqrt(hd)
-    out = ops.paged_attention_prefill(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cu_q.cuda(),
-                                      q_pos0.cuda(), window, scale)
     ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, window, scale)
-    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+    if window > 0:
+        # pages that the window of the first query of the step has wholly passed are given
+        # back: the table says -1 there and the page may hold anything
+        for s, (n, ql) in enumerate(zip(seq_lens, q_lens)):
+            for b in range(max(0, n - ql - window + 1) // page):
+                kc[bt[s, b]] = float("nan")
+                vc[bt[s, b]] = float("nan")
+                bt[s, b] = -1
+    for form in _prefill_forms(page):
+        out = ops.paged_attention_prefill(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cu_q.cuda(),
+                                          q_pos0.cuda(), window, scale, kernel=form)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2,
+                                   msg=lambda m: f"{form}: {m}")
+    ops.check_async_errors()
+
+
+def test_prefill_attention_rescales_when_the_max_grows():
+    """Scores that climb by far more than the lazy-rescale step from tile to tile, then
+    fall: the running max of the tcgen05 form has to follow them."""
+    ops = _ops()
+    heads, kvh, hd, page = 2, 1, 128, 16
+    n = 600
+    q, kc, vc, bt, seq_of, pos = _paged_case(torch.bfloat16, heads, kvh, hd, page, 0, [n], [n],
+                                             seed=5)
+    ramp = torch.cat([torch.linspace(0.05, 3.0, 400), torch.linspace(3.0, 0.2, 200)])
+    for p in range(n):
+        kc[bt[0, p // page], :, p % page] *= ramp[p]
+    cu_q = torch.tensor([0, n], dtype=torch.int32)
+    q_pos0 = torch.tensor([0], dtype=torch.int32)
+    ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, 0, 1.0)
+    for form in ("mma", "tc"):
+        out = ops.paged_attention_prefill(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cu_q.cuda(),
+                                          q_pos0.cuda(), 0, 1.0, kernel=form)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=3e-2, atol=3e-2,
+                                   msg=lambda m: f"{form}: {m}")
+    ops.check_async_errors()
 
 
 def test_prefill_attention_window_edge_and_far_key():
@@ -499,6 +537,7 @@ def test_prefill_attention_window_edge_and_far_key():
         q[qrow, 0] = (key * 4).to(torch.bfloat16)
         cu_q = torch.tensor([0, ql], dtype=torch.int32)
         q_pos0 = torch.tensor([n - ql], dtype=torch.int32)
-        out = ops.paged_attention_prefill(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cu_q.cuda(),
-                                          q_pos0.cuda(), window, 1.0)
-        assert (out[qrow, 0, 0].item() > 0.9) == expect, (window, which, qrow)
+        for form in ("mma", "tc"):
+            out = ops.paged_attention_prefill(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(),
+                                              cu_q.cuda(), q_pos0.cuda(), window, 1.0, kernel=form)
+            assert (out[qrow, 0, 0].item() > 0.9) == expect, (form, window, which, qrow)
