@@ -16,14 +16,15 @@
 //              next scores while the softmax warps are busy with the current ones;
 //   warps 2-5  softmax: a thread holds one query row; it reads the row of S with
 //              tcgen05.ld, masks, keeps the running max and sum, writes P as bf16
-//              into a swizzled shared-memory tile (the A operand of P V), and at the
-//              end scales O by 1 / sum and stores it.
+//              back into the columns of tensor memory that S came from (P V takes
+//              its A operand from there), and at the end scales O by 1 / sum and
+//              stores it.
 // The running max is updated lazily: O (in tensor memory) is rescaled only when some
 // row's max grew by more than 2^8 since the last rescale, the exponent in between is
 // taken against the older max, which changes nothing in exact arithmetic and keeps
 // P within bf16's range.
 //
-// Two blocks fit on an SM (112 KB of shared memory and 256 columns of tensor memory
+// Two blocks fit on an SM (96 KB of shared memory and 256 columns of tensor memory
 // each), so one block's softmax overlaps the other's MMAs.  Every mbarrier wait is
 // bounded; a wait that ran out records a code (21: copies, 22: MMA, 23: softmax) in
 // the caller's status word and the block runs to its end (its output is then not
@@ -42,8 +43,8 @@
 enum { FA_ERR_COPY = 21, FA_ERR_MMA = 22, FA_ERR_SOFTMAX = 23, FA_ERR_ALIGN = 24 };
 
 struct FaBars {
-  unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2],
-      p_ready, o_done;
+  unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready,
+      o_done;
   unsigned tmem_holder;
   int abort_flag;
 };
@@ -68,9 +69,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   constexpr int Q_HALF = FA_BM * 128;
   constexpr int KV_TILE = FA_BN * HD * 2;
   constexpr int KV_HALF = FA_BN * 128;
-  constexpr int P_BYTES = FA_BM * FA_BN * 2;
   constexpr unsigned TMEM_COLS = 256;
-  constexpr unsigned S_COL = HD;                 // O: columns [0, HD); S buffers after it
+  // O: columns [0, HD); then two S buffers of 64 columns; P_j overwrites the first 32
+  // columns of S_j's buffer
+  constexpr unsigned S_COL = HD;
   // kind::f16, D fp32, A and B bf16; S: both K-major, N = 64; P V: B is MN-major, N = HD
   constexpr unsigned IDESC_S =
       (1u << 4) | (1u << 7) | (1u << 10) | ((FA_BN >> 3) << 17) | ((FA_BM >> 4) << 24);
@@ -81,8 +83,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   unsigned char* Qs = smem;                     // so this starts on a 1024-byte mark
   unsigned char* Ks = Qs + Q_BYTES;             // [2][halves][64 keys][128 B]
   unsigned char* Vs = Ks + 2 * KV_TILE;
-  unsigned char* Ps = Vs + 2 * KV_TILE;         // [128 queries][128 B]
-  FaBars* bars = reinterpret_cast<FaBars*>(Ps + P_BYTES);
+  FaBars* bars = reinterpret_cast<FaBars*>(Vs + 2 * KV_TILE);
 
   // which sequence and which 128-query tile of it; heavy tiles first (see the
   // mma.sync kernel)
@@ -123,9 +124,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&bars->v_full[i], 1);
       mbar_init(&bars->v_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->s_empty[i], 4);          // one arrival per softmax warp
     }
-    mbar_init(&bars->p_ready, 4);
+    mbar_init(&bars->p_ready, 4);               // one arrival per softmax warp
     mbar_init(&bars->o_done, 1);
     bars->abort_flag = 0;
     mbar_init_fence();
@@ -207,7 +207,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       auto issue_s = [&](int j) {      // S_j = Q K_j^T into S buffer j & 1
         const int st = j & 1;
         if (!mbar_wait(&bars->k_full[st], (j >> 1) & 1, abortp)) return false;
-        if (!mbar_wait(&bars->s_empty[st], ((j >> 1) & 1) ^ 1, abortp)) return false;
+        // the buffer's last reader, P_{j-2} V_{j-2}, was issued before this: the tensor
+        // pipe keeps the order
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
@@ -233,11 +234,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         tc_fence_after();
 #pragma unroll
         for (int k4 = 0; k4 < FA_BN / 16; ++k4) {
-          // 16 keys further along K: 32 bytes inside P's swizzled row, two 8-key groups
-          // (2048 bytes) down V's tile
-          const unsigned long long pd = umma_desc(Ps) + 2 * k4;
+          // 16 keys further along K: 8 columns of packed P, two 8-key groups (2048
+          // bytes) down V's tile
           const unsigned long long vd = umma_desc_mn(Vs + st * KV_TILE, KV_HALF, 1024) + 128 * k4;
-          tc_mma(tmem_base, pd, vd, IDESC_PV, (j > 0 || k4 > 0) ? 1u : 0u);
+          tc_mma_ts(tmem_base, tmem_base + S_COL + st * FA_BN + 8 * k4, vd, IDESC_PV,
+                    (j > 0 || k4 > 0) ? 1u : 0u);
         }
         tc_commit(&bars->v_empty[st]);
         tc_commit(&bars->o_done);
@@ -261,9 +262,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       float sc[FA_BN];
       tc_ld32(lane_addr + S_COL + st * FA_BN, sc);
       tc_ld32(lane_addr + S_COL + st * FA_BN + 32, sc + 32);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_empty[st]);
       const int kbase = kt0 + j * FA_BN;
       const bool need_mask = (kbase + FA_BN - 1 > pos0) || kbase < kv_lo ||
                              (window > 0 && kbase < pmax - window + 1);
@@ -290,22 +288,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         l_run *= corr;
       }
       const float base = m_ref == -INFINITY ? 0.f : m_ref;
-      unsigned pk[FA_BN / 2];
+      float pk[FA_BN / 2];          // bf16 pairs, as the bit patterns tcgen05.st takes
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < FA_BN; i += 2) {
         const float p0 = fa_exp2(sc[i] - base), p1 = fa_exp2(sc[i + 1] - base);
         sum += p0 + p1;
         __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-        pk[i >> 1] = *reinterpret_cast<unsigned*>(&v);
+        pk[i >> 1] = __uint_as_float(*reinterpret_cast<unsigned*>(&v));
       }
       l_run += sum;
-      // P's tile and O are free once the previous P V has completed
       if (j > 0) {
+        // O may be touched once the previous P V has completed.  Every phase of this
+        // barrier is waited for, in order, also when nothing is rescaled: a parity
+        // wait that skipped a phase would take an older completion for the one it wants.
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_done, (j - 1) & 1, abortp));
         if (!ok) break;
-        tc_fence_after();
         if (rescale) {
+          tc_fence_after();
 #pragma unroll
           for (int c0 = 0; c0 < HD; c0 += 32) {
             float o[32];
@@ -316,11 +316,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
       }
-#pragma unroll
-      for (int c = 0; c < FA_BN / 8; ++c)
-        *reinterpret_cast<uint4*>(Ps + row * 128 + ((c ^ (row & 7)) << 4)) =
-            make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-      fence_proxy_async();
+      tc_st32(lane_addr + S_COL + st * FA_BN, pk);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_ready);
@@ -384,7 +380,7 @@ static int launch_prefill_tc(const void* q, const void* kc, const void* vc, long
   if (rc != IX_OK) return rc;
   rc = ix_tensor_map_bf16_2d(&map_v, vc, cache_rows, HD, 64, page_size);
   if (rc != IX_OK) return rc;
-  const int smem = FA_BM * HD * 2 + 4 * FA_BN * HD * 2 + FA_BM * FA_BN * 2 + (int)sizeof(FaBars);
+  const int smem = FA_BM * HD * 2 + 4 * FA_BN * HD * 2 + (int)sizeof(FaBars);
   auto kern = attn_prefill_tc_kernel<HD>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return (int)e;

@@ -20,6 +20,18 @@ __device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long adesc
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
       : "memory");
 }
+// The same with the A operand read from tensor memory (a row per lane, two 16-bit
+// elements along K per 32-bit column).
+__device__ __forceinline__ void tc_mma_ts(unsigned tmem_d, unsigned tmem_a,
+                                          unsigned long long bdesc, unsigned idesc,
+                                          unsigned accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
 __device__ __forceinline__ void tc_commit(unsigned long long* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
