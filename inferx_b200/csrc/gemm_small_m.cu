@@ -58,17 +58,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
   constexpr int D = KSPLIT == 1 ? (DUAL ? 4 : (NT >= 4 ? 4 : 8)) : (DUAL ? 2 : (NT >= 4 ? 2 : 4));
   __shared__ float red[KSPLIT > 1 ? (DUAL ? 2 : 1) : 1][KSPLIT > 1 ? SM_WARPS : 1]
                       [KSPLIT > 1 ? NT : 1][4][32];
-  IX_PDL_WAIT();
   const int e = blockIdx.y;
-  int lo, hi;
-  if (offsets) {
-    lo = offsets[e];
-    hi = offsets[e + 1];
-  } else {
-    lo = 0;
-    hi = M_single;
-  }
-  if (lo >= hi) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int tile = warp / KSPLIT, ks = warp % KSPLIT;
@@ -83,6 +73,36 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
   const int ksteps = (K + 31) >> 5;
   const int my_steps = ksteps > ks ? (ksteps - ks + KSPLIT - 1) / KSPLIT : 0;
   const uint4 zero = make_uint4(0, 0, 0, 0);
+  // a ring of D k-steps in registers: weights and the matching activations
+  uint4 va[D], vb[D], vua[DUAL ? D : 1], vub[DUAL ? D : 1], vx[D][NT];
+  auto fetch_w = [&](int u, int idx) {
+    const int kb = (ks + idx * KSPLIT) * 32 + t * 8;
+    const bool kok = idx < my_steps && kb < K;
+    va[u] = (kok && ja_ok) ? ld_stream16(wa + kb) : zero;
+    vb[u] = (kok && jb_ok) ? ld_stream16(wb + kb) : zero;
+    if (DUAL) {
+      vua[u] = (kok && ja_ok) ? ld_stream16(ua + kb) : zero;
+      vub[u] = (kok && jb_ok) ? ld_stream16(ub + kb) : zero;
+    }
+  };
+  // A single matrix (no groups) is wanted whatever the predecessor in the stream wrote,
+  // and weights are never written on the device: the first loads of the weight stream
+  // are issued before the wait on the predecessor, so they are in flight while it drains.
+  const bool early = offsets == nullptr;
+  if (early) {
+#pragma unroll
+    for (int u = 0; u < D; ++u) fetch_w(u, u);
+  }
+  IX_PDL_WAIT();
+  int lo, hi;
+  if (offsets) {
+    lo = offsets[e];
+    hi = offsets[e + 1];
+  } else {
+    lo = 0;
+    hi = M_single;
+  }
+  if (lo >= hi) return;
 
   for (int r0 = lo; r0 < hi; r0 += 8 * NT) {
     const bf16* xrow[NT];
@@ -102,23 +122,24 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
         acc[i][c] = 0.f;
         if (DUAL) acc2[i][c] = 0.f;
       }
-    // a ring of D k-steps in registers: weights and the matching activations
-    uint4 va[D], vb[D], vua[DUAL ? D : 1], vub[DUAL ? D : 1], vx[D][NT];
-    auto fetch = [&](int u, int idx) {
+    auto fetch_x = [&](int u, int idx) {
       const int kb = (ks + idx * KSPLIT) * 32 + t * 8;
       const bool kok = idx < my_steps && kb < K;
-      va[u] = (kok && ja_ok) ? ld_stream16(wa + kb) : zero;
-      vb[u] = (kok && jb_ok) ? ld_stream16(wb + kb) : zero;
-      if (DUAL) {
-        vua[u] = (kok && ja_ok) ? ld_stream16(ua + kb) : zero;
-        vub[u] = (kok && jb_ok) ? ld_stream16(ub + kb) : zero;
-      }
 #pragma unroll
       for (int i = 0; i < NT; ++i)
         vx[u][i] = (kok && xok[i]) ? *reinterpret_cast<const uint4*>(xrow[i] + kb) : zero;
     };
+    auto fetch = [&](int u, int idx) {
+      fetch_w(u, idx);
+      fetch_x(u, idx);
+    };
+    if (early && r0 == lo) {
 #pragma unroll
-    for (int u = 0; u < D; ++u) fetch(u, u);
+      for (int u = 0; u < D; ++u) fetch_x(u, u);
+    } else {
+#pragma unroll
+      for (int u = 0; u < D; ++u) fetch(u, u);
+    }
     for (int base = 0; base < my_steps; base += D) {
 #pragma unroll
       for (int u = 0; u < D; ++u) {
