@@ -398,7 +398,8 @@ def test_decode_attention_finds_one_far_key():
 
 
 @pytest.mark.parametrize("T,H,I,E,k", [(1, 64, 32, 4, 2), (9, 200, 72, 8, 3), (40, 96, 48, 60, 4),
-                                       (16, 2048, 1408, 6, 2)])
+                                       (16, 2048, 1408, 6, 2), (8, 264, 328, 60, 4),
+                                       (3, 1000, 256, 33, 2), (20, 512, 520, 5, 3)])
 def test_small_m_grouped_experts(T, H, I, E, k):
     """The weight-streaming kernel (few rows per expert) against the plain statement,
     including an expert with more rows than one chunk holds."""
@@ -421,12 +422,27 @@ def test_small_m_grouped_experts(T, H, I, E, k):
                 row[j] = e
             idx[t] = torch.tensor(row, dtype=torch.int32)
     off, rows, dest = host_ops.moe_dispatch(idx, E)
-    act = ops.gemm_small_m(x.cuda(), wgu.cuda(), rows.cuda(), off.cuda(), True, rows.numel())
     ract = host_ops.grouped_gate_up_swiglu(x, rows, off, wgu)
-    torch.testing.assert_close(act.cpu().float(), ract.float(), **_tol(dtype))
-    y = ops.gemm_small_m(ract.cuda(), wd.cuda(), None, off.cuda(), False, ract.shape[0])
     ry = host_ops.grouped_down(ract, off, wd)
-    torch.testing.assert_close(y.cpu().float(), ry.float(), **_tol(dtype))
+    forms = [ops.gemm_small_m]
+    if H >= 256 and I >= 256:       # the persistent form splits K over eight warps
+        forms.append(ops.gemm_stream_grouped)
+    for form in forms:
+        for per_pass in (8, 16):
+            act = form(x.cuda(), wgu.cuda(), rows.cuda(), off.cuda(), True, rows.numel(),
+                       rows_per_pass=per_pass)
+            torch.testing.assert_close(act.cpu().float(), ract.float(), **_tol(dtype))
+            y = form(ract.cuda(), wd.cuda(), None, off.cuda(), False, ract.shape[0],
+                     rows_per_pass=per_pass)
+            torch.testing.assert_close(y.cpu().float(), ry.float(), **_tol(dtype))
+
+
+def test_stream_grouped_refuses_short_k():
+    ops = _ops()
+    with pytest.raises(ops.KernelError):
+        ops.gemm_stream_grouped(torch.zeros(4, 128, dtype=torch.bfloat16).cuda(),
+                                torch.zeros(2, 16, 128, dtype=torch.bfloat16).cuda(), None,
+                                torch.tensor([0, 2, 4], dtype=torch.int32).cuda(), False, 4)
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 50, 72), (8, 130, 200), (13, 64, 256), (16, 1000, 2048),
