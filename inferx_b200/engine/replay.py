@@ -31,8 +31,15 @@ class ReplayError(RuntimeError):
     pass
 
 
-def pages_for(max_tokens: int, page_size: int) -> int:
-    return max(1, -(-int(max_tokens) // page_size))
+def pages_for(max_tokens: int, page_size: int, max_live: int = 1) -> int:
+    """Pages for live requests that hold ``max_tokens`` tokens in all, each request's
+    count rounded up to a multiple of 64.  A request of k * 64 tokens needs at most
+    k * ceil(64 / page_size) pages, whatever the page size; pages larger than 64 tokens
+    can cost every live request one page more than its share."""
+    units = -(-int(max_tokens) // 64)
+    if page_size <= 64:
+        return max(1, units * -(-64 // page_size))
+    return max(1, -(-units * 64 // page_size) + max_live)
 
 
 class ReplaySession:
@@ -40,7 +47,8 @@ class ReplaySession:
                  max_live: int = 8, device: str = "cuda", ops=None, use_graphs: bool = False):
         _, model = load_model(model_dir, dtype=dtype, device=device, ops=ops)
         self.runtime = Runtime(model, page_size=page_size,
-                               num_pages=pages_for(max_tokens, page_size), max_slots=max_live,
+                               num_pages=pages_for(max_tokens, page_size, max_live),
+                               max_slots=max_live,
                                use_graphs=use_graphs)
         self.manager = self.runtime.manager
         self.executor = self.runtime.executor
