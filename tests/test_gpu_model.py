@@ -110,15 +110,14 @@ def test_head_size_64_over_page_sizes(tmp_path):
     """Head size 64 with a 70-token window on the second layer, over the page sizes the
     TMA-fed kernels take (8, 32, 64) and one they do not (12, which falls to the cp.async
     forms): prompts longer than the window, decoded on, and mixed with page reuse.  Each
-    against the plain model; the three TMA page sizes also against one another, far more
-    tightly (the same kernels and arithmetic; only where a key lies differs)."""
+    against the plain model.  (Not against one another: the number of key splits follows
+    the width of the block table, so page sizes differ by rounding.)"""
     d = mc.make_model_dir(HD64, tmp_path / "m", 6, dtype="bfloat16")
     reqs = mc.make_requests(HD64, [300, 130, 64, 9], 6)
     ref = mc.reference_rows(d, reqs)
     bound = mc.bf16_bound(d, reqs)
     for kind in ("tail", "mixed"):
         steps = mc.TRACE_KINDS[kind](reqs)
-        first = None
         for page in (8, 32, 64, 12):
             sess = ReplaySession(d, "bfloat16", traces.peak_tokens(steps), page_size=page,
                                  max_live=4, use_graphs=(kind == "tail"))
@@ -126,10 +125,6 @@ def test_head_size_64_over_page_sizes(tmp_path):
             sess.executor.poll_errors()
             worst = mc.compare(rows, ref, bound, f"hd64/page{page}/{kind}")
             print(f"hd64/page{page}/{kind}: worst relative error {worst:.3e} (bound {bound:.3e})")
-            if first is None:
-                first = rows
-            elif page != 12:
-                mc.compare(rows, first, 2e-3, f"hd64/page{page} against page 8/{kind}")
 
 
 def test_grouped_query_heads_at_width(tmp_path):
