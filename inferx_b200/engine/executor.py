@@ -69,6 +69,7 @@ class _Layout:
     widths: List[int]          # block-table width per group
     q_lens: List[int]
     kv_lens: List[int]
+    num_decode: int = 0        # sequences with a single token; they come first
 
 
 @dataclass
@@ -116,7 +117,12 @@ class Executor:
         slots: List[List[int]] = [[] for _ in range(n_groups)]
         ps = mgr.page_size
         vocab = self.vocab
-        for s, e in enumerate(entries):
+        # single tokens first, prompt portions after them, each kind in the order given:
+        # attention can then treat the two parts of a mixed batch as two plain batches
+        order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)
+        base_of = [0] * len(entries)
+        for s, i in enumerate(order):
+            e = entries[i]
             rid = e.request
             if rid in seen:
                 raise StepError(f"request {rid!r} appears twice in one step")
@@ -131,7 +137,7 @@ class Executor:
                 raise StepError(
                     f"request {rid!r}: positions {start}..{start + n - 1} exceed the "
                     f"{mgr.capacity(rid)} tokens its pages hold (reserve first)")
-            base = len(token_ids)
+            base_of[i] = len(token_ids)
             for tok in e.tokens:
                 tok = int(tok)
                 if not (0 <= tok < vocab):
@@ -139,11 +145,9 @@ class Executor:
                                     f"vocabulary of {vocab}")
                 token_ids.append(tok)
             for w in e.want:
-                w = int(w)
-                if not (0 <= w < n):
-                    raise StepError(f"request {rid!r}: wanted place {w} is not among "
+                if not (0 <= int(w) < n):
+                    raise StepError(f"request {rid!r}: wanted place {int(w)} is not among "
                                     f"its {n} tokens")
-                logit_rows.append(base + w)
             for g in range(n_groups):
                 table = mgr.table(rid, g)
                 sl = slots[g]
@@ -159,9 +163,13 @@ class Executor:
             q_pos0.append(start)
             kv_len.append(start + n)
             state_slot.append(mgr.slot(rid))
+        for i, e in enumerate(entries):      # logits come back in the order of the entries
+            logit_rows.extend(base_of[i] + int(w) for w in e.want)
+        num_decode = sum(1 for e in entries if len(e.tokens) == 1)
+        cu_q_prompt = [c - cu_q[num_decode] for c in cu_q[num_decode:]]
         widths, tables = [], []
         for g in range(n_groups):
-            rows = [mgr.table(e.request, g) for e in entries]
+            rows = [mgr.table(entries[i].request, g) for i in order]
             mb = max(1, max(len(r) for r in rows))
             if bucket_tables:
                 mb = _bucket(mb)
@@ -174,6 +182,7 @@ class Executor:
         segs = [token_ids, positions, seq_of_token, cu_q, q_pos0, kv_len, state_slot, logit_rows]
         for g in range(n_groups):
             segs += [slots[g], tables[g]]
+        segs.append(cu_q_prompt)
         offs, total = [], 0
         for sgm in segs:
             offs.append(total)
@@ -181,7 +190,8 @@ class Executor:
         S = len(entries)
         return _Layout(T=len(token_ids), S=S, R=len(logit_rows), segs=segs, offs=offs,
                        total=max(total, 4), widths=widths,
-                       q_lens=[cu_q[i + 1] - cu_q[i] for i in range(S)], kv_lens=kv_len)
+                       q_lens=[cu_q[i + 1] - cu_q[i] for i in range(S)], kv_lens=kv_len,
+                       num_decode=num_decode)
 
     @staticmethod
     def _fill(host: torch.Tensor, lay: _Layout) -> None:
@@ -208,7 +218,8 @@ class Executor:
             seq_of_token=seg(2), cu_q=seg(3), q_pos0=seg(4), kv_len=seg(5), state_slot=seg(6),
             groups=groups, max_q_len=max(lay.q_lens), max_kv_len=max_kv,
             q_lens=list(lay.q_lens), kv_lens=list(lay.kv_lens),
-            all_decode=all(n == 1 for n in lay.q_lens))
+            all_decode=all(n == 1 for n in lay.q_lens), num_decode_seqs=lay.num_decode,
+            cu_q_prompt=seg(8 + 2 * len(mgr.groups)))
         return ctx, (seg(7) if lay.R else None)
 
     def build_context(self, entries: Sequence[StepEntry]):

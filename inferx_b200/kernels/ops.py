@@ -420,7 +420,8 @@ def _tma_decode_applies(q, page: int) -> bool:
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                            block_table: torch.Tensor, kv_len: torch.Tensor, max_kv_len: int,
                            window: int, scale: float, splits: Optional[int] = None,
-                           scalar_kernel: bool = False, kernel: Optional[str] = None):
+                           scalar_kernel: bool = False, kernel: Optional[str] = None,
+                           out: Optional[torch.Tensor] = None):
     """Split-KV attention for a batch in which sequence s brings the one query q[s]
     at position kv_len[s] - 1.  ``kernel`` picks a form ("tma", "mma", "scalar");
     None takes the fastest that applies."""
@@ -454,7 +455,12 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     if splits is None:
         pick = lib.ix_attn_decode_tma_splits if kernel == "tma" else lib.ix_attn_decode_splits
         splits = pick(S, heads, kvh, int(max_kv_len))
-    out = torch.empty_like(q)
+    if out is None:
+        out = torch.empty_like(q)
+    else:
+        _chk("out", out, q.dtype)
+        if out.shape != q.shape:
+            raise KernelError("paged_attention_decode: out must have the query's shape")
     part_o = part_ml = None
     if splits > 1:
         part_o = torch.empty((S, heads, splits, hd), dtype=torch.float32, device=q.device)
@@ -492,7 +498,8 @@ def _tc_prefill_applies(q, page: int) -> bool:
 
 def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                             block_table: torch.Tensor, cu_q: torch.Tensor, q_pos0: torch.Tensor,
-                            window: int, scale: float, kernel: Optional[str] = None):
+                            window: int, scale: float, kernel: Optional[str] = None,
+                            out: Optional[torch.Tensor] = None):
     """Tensor-core attention for a ragged batch: sequence s brings the queries
     q[cu_q[s]:cu_q[s+1]] at positions q_pos0[s], q_pos0[s]+1, ...  ``kernel`` picks a
     form ("tc", "mma"); None takes the fastest that applies."""
@@ -520,7 +527,12 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         raise KernelError(f"paged_attention_prefill: the tcgen05 form takes bf16, head size 64 "
                           f"or 128 and a page of 8, 16, 32 or 64 keys (got {q.dtype}, {hd}, "
                           f"{page})")
-    out = torch.empty_like(q)
+    if out is None:
+        out = torch.empty_like(q)
+    else:
+        _chk("out", out, q.dtype)
+        if out.shape != q.shape:
+            raise KernelError("paged_attention_prefill: out must have the query's shape")
     if kernel == "tc":
         code = _lib().ix_paged_attention_prefill_tc(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), P, _ptr(block_table), _ptr(cu_q),
@@ -549,6 +561,17 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         return paged_attention_decode(q, k_cache, v_cache, block_table, step.kv_len,
                                       step.max_kv_len, window, scale)
     if hd in _PREFILL_HEAD_SIZES.get(q.dtype, ()):
+        nd = getattr(step, "num_decode_seqs", 0)
+        if 0 < nd < step.num_seqs and getattr(step, "cu_q_prompt", None) is not None:
+            # a mixed batch: its single tokens (they come first) go to the split-KV kernel,
+            # which streams their keys at full rate, the prompt portions to the tiled one
+            out = torch.empty_like(q)
+            paged_attention_decode(q[:nd], k_cache, v_cache, block_table[:nd], step.kv_len[:nd],
+                                   step.max_kv_len, window, scale, out=out[:nd])
+            paged_attention_prefill(q[nd:], k_cache, v_cache, block_table[nd:],
+                                    step.cu_q_prompt, step.q_pos0[nd:], window, scale,
+                                    out=out[nd:])
+            return out
         return paged_attention_prefill(q, k_cache, v_cache, block_table, step.cu_q, step.q_pos0,
                                        window, scale)
     return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,

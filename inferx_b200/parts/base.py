@@ -78,6 +78,12 @@ class StepContext:
     q_lens: List[int] = field(default_factory=list)
     kv_lens: List[int] = field(default_factory=list)
     all_decode: bool = False
+    # Sequences that bring a single token come first in the batch: the first
+    # ``num_decode_seqs`` sequences (and tokens).  ``cu_q_prompt`` is ``cu_q`` of the
+    # remaining sequences counted from their own first token, so that a mixer can hand
+    # the two parts of a mixed batch to different kernels without gathering.
+    num_decode_seqs: int = 0
+    cu_q_prompt: Optional[torch.Tensor] = None   # [S - num_decode_seqs + 1] int32
 
 
 @dataclass

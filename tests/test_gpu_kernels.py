@@ -511,6 +511,40 @@ def test_paged_attention_prefill(heads, kvh, hd, page, window):
     ops.check_async_errors()
 
 
+def test_mixed_batch_goes_to_both_attention_kernels():
+    """ops.paged_attention on a batch whose first sequences bring one token each: those
+    go to the split-KV kernel, the prompt portions to the tiled one, and the result is
+    that of the general kernel on the whole batch."""
+    import types
+    ops = _ops()
+    heads, kvh, hd, page, window = 6, 2, 128, 16, 90
+    seq_lens, q_lens = [700, 33, 1, 150, 400, 65], [1, 1, 1, 150, 70, 2]
+    q, kc, vc, bt, seq_of, pos = _paged_case(torch.bfloat16, heads, kvh, hd, page, window,
+                                             seq_lens, q_lens, seed=77)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    nd = 3
+    step = types.SimpleNamespace(
+        num_seqs=len(seq_lens), num_tokens=cu[-1], all_decode=False, num_decode_seqs=nd,
+        seq_of_token=seq_of.cuda(), positions=pos.cuda(),
+        cu_q=torch.tensor(cu, dtype=torch.int32).cuda(),
+        cu_q_prompt=torch.tensor([c - cu[nd] for c in cu[nd:]], dtype=torch.int32).cuda(),
+        q_pos0=torch.tensor([n - ql for n, ql in zip(seq_lens, q_lens)], dtype=torch.int32).cuda(),
+        kv_len=torch.tensor(seq_lens, dtype=torch.int32).cuda(),
+        max_q_len=max(q_lens), max_kv_len=max(seq_lens))
+    scale = 1.0 / math.sqrt(hd)
+    before = ops.LAUNCHES[0]
+    out = ops.paged_attention(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), step, window, scale)
+    assert ops.LAUNCHES[0] - before >= 2      # two kernels (and a merge when keys are split)
+    ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, window, scale)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+    step.num_decode_seqs = 0          # the same through the tiled kernel alone
+    out2 = ops.paged_attention(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), step, window, scale)
+    torch.testing.assert_close(out2.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+    ops.check_async_errors()
+
+
 def test_prefill_attention_rescales_when_the_max_grows():
     """Scores that climb by far more than the lazy-rescale step from tile to tile, then
     fall: the running max of the tcgen05 form has to follow them."""
