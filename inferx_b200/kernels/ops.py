@@ -588,6 +588,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
 
 USE_TCGEN05 = True           # prompt-sized grouped products go to the tcgen05 kernel
+TCGEN05_MAX_EXPERTS = 1024   # its per-expert tile prefix lives in shared memory
 SMALL_M_ROWS_PER_GROUP = 8   # grouped: up to this many rows per expert on average
 SMALL_M_DENSE_ROWS = 32      # dense: up to this many rows stream the weights once
 
@@ -735,7 +736,7 @@ def grouped_gate_up_swiglu(x: torch.Tensor, rows: torch.Tensor, offsets: torch.T
     if per <= SMALL_M_ROWS_PER_GROUP and _streams_weights(x, w_gate_up):
         return gemm_small_m(x, w_gate_up, rows, offsets, True, A,
                             rows_per_pass=8 if per <= 2 else 16)
-    if USE_TCGEN05 and _streams_weights(x, w_gate_up):
+    if USE_TCGEN05 and _streams_weights(x, w_gate_up) and w_gate_up.shape[0] <= TCGEN05_MAX_EXPERTS:
         return grouped_gemm_tc(gather_rows(x, rows), offsets, w_gate_up, True)
     return gemm_generic(x, w_gate_up, rows, offsets, dual=True, num_out_rows=A)
 
@@ -750,7 +751,7 @@ def grouped_down(act: torch.Tensor, offsets: torch.Tensor, w_down: torch.Tensor)
     if per <= SMALL_M_ROWS_PER_GROUP and _streams_weights(act, w_down):
         return gemm_small_m(act, w_down, None, offsets, False, A,
                             rows_per_pass=8 if per <= 2 else 16)
-    if USE_TCGEN05 and _streams_weights(act, w_down):
+    if USE_TCGEN05 and _streams_weights(act, w_down) and w_down.shape[0] <= TCGEN05_MAX_EXPERTS:
         return grouped_gemm_tc(act, offsets, w_down, False)
     return gemm_generic(act, w_down, None, offsets, dual=False, num_out_rows=A)
 
