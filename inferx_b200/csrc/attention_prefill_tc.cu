@@ -55,6 +55,35 @@ __device__ __forceinline__ float fa_exp2(float x) {
   return y;
 }
 
+// Two fp32 operations per instruction (packed f32x2) and a three-input maximum: the
+// softmax warps are bound by instruction issue, so the per-score work is kept to a
+// max, a fused multiply-add, an exp2, an add and half a pack.
+__device__ __forceinline__ void fa_fma2(float& r0, float& r1, float x0, float x1, float s,
+                                        float c) {
+  asm("{ .reg .b64 va, vs, vc, vd;\n\t"
+      "mov.b64 va, {%2, %3};\n\t"
+      "mov.b64 vs, {%4, %4};\n\t"
+      "mov.b64 vc, {%5, %5};\n\t"
+      "fma.rn.f32x2 vd, va, vs, vc;\n\t"
+      "mov.b64 {%0, %1}, vd; }"
+      : "=f"(r0), "=f"(r1)
+      : "f"(x0), "f"(x1), "f"(s), "f"(c));
+}
+__device__ __forceinline__ void fa_add2(float& a0, float& a1, float b0, float b1) {
+  asm("{ .reg .b64 va, vb, vd;\n\t"
+      "mov.b64 va, {%0, %1};\n\t"
+      "mov.b64 vb, {%2, %3};\n\t"
+      "add.rn.f32x2 vd, va, vb;\n\t"
+      "mov.b64 {%0, %1}, vd; }"
+      : "+f"(a0), "+f"(a1)
+      : "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ float fa_max3(float a, float b, float c) {
+  float m;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(a), "f"(b), "f"(c));
+  return m;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(FA_THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -265,18 +294,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       const int kbase = kt0 + j * FA_BN;
       const bool need_mask = (kbase + FA_BN - 1 > pos0) || kbase < kv_lo ||
                              (window > 0 && kbase < pmax - window + 1);
-      float mx = -INFINITY;
+      if (need_mask) {
 #pragma unroll
-      for (int i = 0; i < FA_BN; ++i) {
-        float v = sc[i] * scale_log2e;
-        if (need_mask) {
+        for (int i = 0; i < FA_BN; ++i) {
           const int kp = kbase + i;
-          if (kp > pos || kp < lo_r) v = -INFINITY;
+          if (kp > pos || kp < lo_r) sc[i] = -INFINITY;
         }
-        sc[i] = v;
-        mx = fmaxf(mx, v);
       }
-      const float m_new = fmaxf(m_ref, mx);
+      // of the raw scores (the scale is positive); two chains, so that one max does not
+      // wait for the one before it
+      float mxa = -INFINITY, mxb = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < FA_BN; i += 4) {
+        mxa = fa_max3(mxa, sc[i], sc[i + 1]);
+        mxb = fa_max3(mxb, sc[i + 2], sc[i + 3]);
+      }
+      const float mx = fmaxf(mxa, mxb);
+      const float m_new = fmaxf(m_ref, mx * scale_log2e);
       // rescale when this row's max has outgrown the reference by more than the step
       // (or when the row sees its first key); the decision is the warp's
       const bool grow = m_new > m_ref + FA_RESCALE_STEP || (m_ref == -INFINITY && m_new > m_ref);
@@ -287,16 +321,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         m_ref = m_new;
         l_run *= corr;
       }
-      const float base = m_ref == -INFINITY ? 0.f : m_ref;
+      const float nbase = m_ref == -INFINITY ? 0.f : -m_ref;
       float pk[FA_BN / 2];          // bf16 pairs, as the bit patterns tcgen05.st takes
-      float sum = 0.f;
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < FA_BN; i += 2) {
-        const float p0 = fa_exp2(sc[i] - base), p1 = fa_exp2(sc[i + 1] - base);
-        sum += p0 + p1;
-        __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+      for (int i = 0; i < FA_BN; i += 4) {
+        float a0, a1, a2, a3;
+        fa_fma2(a0, a1, sc[i], sc[i + 1], scale_log2e, nbase);   // -inf stays -inf
+        fa_fma2(a2, a3, sc[i + 2], sc[i + 3], scale_log2e, nbase);
+        const float p0 = fa_exp2(a0), p1 = fa_exp2(a1), p2 = fa_exp2(a2), p3 = fa_exp2(a3);
+        fa_add2(sum0, sum1, p0, p1);
+        fa_add2(sum2, sum3, p2, p3);
+        __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1), v2 = __floats2bfloat162_rn(p2, p3);
         pk[i >> 1] = __uint_as_float(*reinterpret_cast<unsigned*>(&v));
+        pk[(i >> 1) + 1] = __uint_as_float(*reinterpret_cast<unsigned*>(&v2));
       }
+      const float sum = (sum0 + sum1) + (sum2 + sum3);
       l_run += sum;
       if (j > 0) {
         // O may be touched once the previous P V has completed.  Every phase of this
