@@ -111,7 +111,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
   constexpr int STAGES = TC_SMEM_STAGES / STAGE_BYTES;
   constexpr int ACC_COLS = BT * (DUAL ? 2 : 1);          // one accumulator set
   constexpr int NBUF = ACC_COLS * 2 <= 512 ? 2 : 1;
-  constexpr unsigned TMEM_COLS = ACC_COLS * NBUF;
+  // tcgen05.alloc takes a power of two of at least 32 columns
+  constexpr unsigned TMEM_NEED = ACC_COLS * NBUF;
+  constexpr unsigned TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128
+                                 : TMEM_NEED <= 256 ? 256 : 512;
+  static_assert(TMEM_NEED <= 512, "tensor memory has 512 columns");
   static_assert(STAGES >= 2 && STAGES <= 8, "ring depth");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles =
@@ -356,9 +360,10 @@ IX_API int ix_grouped_gemm_tc(const void* a, const int* offsets, const void* w, 
   if ((long long)E * w_rows > 0x7fffffffLL) return IX_ERR_SIZE;
   // SwiGLU form: 128-token tiles always, since two accumulator sets of that width fit
   // in tensor memory and the epilogue (exp, divide) of one item then overlaps the next
-  // item's MMAs; with 256-token tiles it could not, and that cost more than reading the
-  // weights a second time out of L2.  Plain form: 256-token tiles (each weight tile
-  // read once) unless experts have so few rows that the narrow tile's deeper ring wins.
+  // item's MMAs; with 160- or 256-token tiles (one set) it cannot, and that cost more
+  // than reading the weights a second time out of L2 (183 and 187 us against 164 us at
+  // 2048 tokens).  Plain form: 256-token tiles (each weight tile read once) unless
+  // experts have so few rows that the narrow tile's deeper ring wins.
   if (dual)
     return launch_tc<true, 128>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream);
   if (A_rows / E <= 96)
