@@ -397,6 +397,32 @@ def test_decode_attention_finds_one_far_key():
             torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=1.0)
 
 
+def test_decode_attention_long_context_many_splits():
+    """Twenty thousand keys of one sequence (dozens of key splits, more than a thousand
+    pages of 8 in a shuffled table): one marked key near either end and in the middle."""
+    ops = _ops()
+    heads, kvh, hd, page = 8, 1, 64, 8
+    n = 20011
+    q, kc, vc, bt, seq_of, pos = _paged_case(torch.bfloat16, heads, kvh, hd, page, 0, [n], [1],
+                                             seed=9)
+    kc = kc * 0.01
+    key = torch.randn(hd)
+    q[0, :, :] = (key * 2).to(torch.bfloat16)
+    for far in (3, 9999, 20010):
+        kcf, vcf = kc.clone(), vc.clone()
+        kcf[bt[0, far // page], :, far % page] = key.to(torch.bfloat16)
+        vcf[bt[0, far // page], :, far % page, 0] = 1000.0
+        ref = host_ops.paged_attention_generic(q, kcf, vcf, bt, seq_of, pos, 0, 1.0)
+        assert ref[0, 0, 0] > 900
+        for form in ("tma", "mma", "scalar"):
+            out = ops.paged_attention_decode(q.cuda(), kcf.cuda(), vcf.cuda(), bt.cuda(),
+                                             torch.tensor([n], dtype=torch.int32).cuda(), n, 0,
+                                             1.0, kernel=form)
+            torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=1.0,
+                                       msg=lambda m: f"{form}, key {far}: {m}")
+    ops.check_async_errors()
+
+
 @pytest.mark.parametrize("T,H,I,E,k", [(1, 64, 32, 4, 2), (9, 200, 72, 8, 3), (40, 96, 48, 60, 4),
                                        (16, 2048, 1408, 6, 2), (8, 264, 328, 60, 4),
                                        (3, 1000, 256, 33, 2), (20, 512, 520, 5, 3)])
