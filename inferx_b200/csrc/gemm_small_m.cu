@@ -51,7 +51,8 @@ template <typename TO, bool DUAL, int NT, int KSPLIT>
 __global__ void __launch_bounds__(SM_THREADS, (NT >= 4 || (NT >= 2 && KSPLIT == 1)) ? 1 : 2)
 gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
                     const int* __restrict__ offsets, const bf16* __restrict__ w,
-                    TO* __restrict__ out, int M_single, int N, int K, long long w_expert_stride) {
+                    TO* __restrict__ out, int M_single, int N, int K, long long w_expert_stride,
+                    int offsets_settled) {
   constexpr int TILES = SM_WARPS / KSPLIT;        // 16-column tiles per block
   // k-steps kept in flight per warp: deep when a warp streams all of K for its tile,
   // shallower when K is split over warps (more warps resident instead)
@@ -85,24 +86,28 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
       vub[u] = (kok && jb_ok) ? ld_stream16(ub + kb) : zero;
     }
   };
-  // A single matrix (no groups) is wanted whatever the predecessor in the stream wrote,
-  // and weights are never written on the device: the first loads of the weight stream
-  // are issued before the wait on the predecessor, so they are in flight while it drains.
-  const bool early = offsets == nullptr;
+  // Weights are never written on the device, so the first loads of the weight stream can
+  // go out before the wait on the predecessor in the stream and be in flight while it
+  // drains: always for a single matrix (it is wanted whatever the predecessor wrote), and
+  // for groups when the caller says that `offsets` was written at least two launches
+  // back (the predecessor itself waited for that launch before it let this one start).
+  const bool early = offsets == nullptr || offsets_settled != 0;
+  int lo = 0, hi = M_single;
   if (early) {
+    if (offsets) {
+      lo = offsets[e];
+      hi = offsets[e + 1];
+    }
+    if (lo >= hi) return;
 #pragma unroll
     for (int u = 0; u < D; ++u) fetch_w(u, u);
   }
   IX_PDL_WAIT();
-  int lo, hi;
-  if (offsets) {
+  if (!early) {
     lo = offsets[e];
     hi = offsets[e + 1];
-  } else {
-    lo = 0;
-    hi = M_single;
+    if (lo >= hi) return;
   }
-  if (lo >= hi) return;
 
   for (int r0 = lo; r0 < hi; r0 += 8 * NT) {
     const bf16* xrow[NT];
@@ -203,41 +208,45 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
 
 template <typename TO, bool DUAL, int NT, int KSPLIT>
 static int launch_small_m2(const void* x, const int* rows, const int* offsets, const void* w,
-                           void* out, int M, int N, int K, int E, cudaStream_t stream) {
+                           void* out, int M, int N, int K, int E, int settled,
+                           cudaStream_t stream) {
   if (E > 65535) return IX_ERR_SIZE;
   const long long w_rows = DUAL ? 2LL * N : N;
   constexpr int TILES = SM_WARPS / KSPLIT;
   dim3 grid((N + 16 * TILES - 1) / (16 * TILES), E);
   ix_launch(gemm_small_m_kernel<TO, DUAL, NT, KSPLIT>, grid, dim3(SM_THREADS), 0, stream,
             (const bf16*)x, rows, offsets, (const bf16*)w, (TO*)out, offsets ? 0 : M, N, K,
-            w_rows * K);
+            w_rows * K, settled);
   return ix_launch_status();
 }
 
 template <typename TO, bool DUAL, int NT>
 static int launch_small_m(const void* x, const int* rows, const int* offsets, const void* w,
-                          void* out, int M, int N, int K, int E, int active_groups,
+                          void* out, int M, int N, int K, int E, int active_groups, int settled,
                           cudaStream_t stream) {
   // enough warps to keep every SM streaming: split K over warps when there are few tiles
   const long long tiles = (long long)((N + 15) / 16) * (active_groups > 0 ? active_groups : 1);
   int ksplit = 1;
   while (ksplit < 8 && tiles * ksplit < 148 * 8) ksplit *= 2;
   if (ksplit == 1)
-    return launch_small_m2<TO, DUAL, NT, 1>(x, rows, offsets, w, out, M, N, K, E, stream);
+    return launch_small_m2<TO, DUAL, NT, 1>(x, rows, offsets, w, out, M, N, K, E, settled, stream);
   if (ksplit == 2)
-    return launch_small_m2<TO, DUAL, NT, 2>(x, rows, offsets, w, out, M, N, K, E, stream);
+    return launch_small_m2<TO, DUAL, NT, 2>(x, rows, offsets, w, out, M, N, K, E, settled, stream);
   if (ksplit == 4)
-    return launch_small_m2<TO, DUAL, NT, 4>(x, rows, offsets, w, out, M, N, K, E, stream);
-  return launch_small_m2<TO, DUAL, NT, 8>(x, rows, offsets, w, out, M, N, K, E, stream);
+    return launch_small_m2<TO, DUAL, NT, 4>(x, rows, offsets, w, out, M, N, K, E, settled, stream);
+  return launch_small_m2<TO, DUAL, NT, 8>(x, rows, offsets, w, out, M, N, K, E, settled, stream);
 }
 
 // x: [*, K] bf16; w: [E, N (or 2N when dual), K] bf16; out: [rows, N] bf16 or fp32.
 // offsets == null: one matrix (E must be 1) with M rows.  rows_per_pass: 8, 16 or 32
 // activation rows handled per pass over a group's weights.  active_groups: how many
 // groups are expected to have rows (a hint for how to spread the work; 0 = all).
+// offsets_settled: nonzero when `offsets` was written at least two launches back in the
+// stream, which lets a grouped launch start its weight stream before its wait.
 IX_API int ix_gemm_small_m(const void* x, const int* rows, const int* offsets, const void* w,
                            void* out, int out_dtype, int dual, int M, int N, int K, int E,
-                           int rows_per_pass, int active_groups, cudaStream_t stream) {
+                           int rows_per_pass, int active_groups, int offsets_settled,
+                           cudaStream_t stream) {
   if (N <= 0 || K <= 0 || E <= 0) return IX_ERR_SIZE;
   if (K % 8 != 0) return IX_ERR_UNSUPPORTED;
   if (!offsets && E != 1) return IX_ERR_SIZE;
@@ -247,9 +256,9 @@ IX_API int ix_gemm_small_m(const void* x, const int* rows, const int* offsets, c
   if (active_groups <= 0 || active_groups > E) active_groups = E;
 #define IX_SM(TO, D)                                                                          \
   do {                                                                                        \
-    if (nt == 4) return launch_small_m<TO, D, 4>(x, rows, offsets, w, out, M, N, K, E, active_groups, stream); \
-    if (nt == 2) return launch_small_m<TO, D, 2>(x, rows, offsets, w, out, M, N, K, E, active_groups, stream); \
-    return launch_small_m<TO, D, 1>(x, rows, offsets, w, out, M, N, K, E, active_groups, stream); \
+    if (nt == 4) return launch_small_m<TO, D, 4>(x, rows, offsets, w, out, M, N, K, E, active_groups, offsets_settled, stream); \
+    if (nt == 2) return launch_small_m<TO, D, 2>(x, rows, offsets, w, out, M, N, K, E, active_groups, offsets_settled, stream); \
+    return launch_small_m<TO, D, 1>(x, rows, offsets, w, out, M, N, K, E, active_groups, offsets_settled, stream); \
   } while (0)
   if (out_dtype == IX_BF16) {
     if (dual) IX_SM(bf16, true);

@@ -596,8 +596,11 @@ SMALL_M_DENSE_ROWS = 32      # dense: up to this many rows stream the weights on
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor],
                  offsets: Optional[torch.Tensor], dual: bool, num_out_rows: int,
                  out_dtype: Optional[torch.dtype] = None, rows_per_pass: int = 8,
-                 active_groups: int = 0):
-    """Weight-streaming product for few rows per weight matrix (bf16 inputs)."""
+                 active_groups: int = 0, offsets_settled: bool = False):
+    """Weight-streaming product for few rows per weight matrix (bf16 inputs).
+    ``offsets_settled``: the kernel that wrote ``offsets`` is at least two launches back
+    in this stream (so the launch may read it, and start on its weights, before waiting
+    for its predecessor)."""
     _chk("x", x, torch.bfloat16)
     _chk("w", w, torch.bfloat16)
     _chk("rows", rows, torch.int32, optional=True)
@@ -612,7 +615,7 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor],
         _ptr(x), _ptr(rows), _ptr(offsets), _ptr(w), _ptr(out),
         F32 if out_dtype == torch.float32 else BF16, 1 if dual else 0,
         0 if offsets is not None else x.shape[0], N, K, E, rows_per_pass,
-        active_groups or min(E, num_out_rows), _stream())
+        active_groups or min(E, num_out_rows), 1 if offsets_settled else 0, _stream())
     _check(code, "gemm_small_m")
     _count()
     return out
@@ -741,8 +744,11 @@ def grouped_gate_up_swiglu(x: torch.Tensor, rows: torch.Tensor, offsets: torch.T
     return gemm_generic(x, w_gate_up, rows, offsets, dual=True, num_out_rows=A)
 
 
-def grouped_down(act: torch.Tensor, offsets: torch.Tensor, w_down: torch.Tensor):
-    """y[r] = act[r] . Wd[e]^T with ``w_down`` [E, H, I]."""
+def grouped_down(act: torch.Tensor, offsets: torch.Tensor, w_down: torch.Tensor,
+                 offsets_settled: bool = False):
+    """y[r] = act[r] . Wd[e]^T with ``w_down`` [E, H, I].  ``offsets_settled``: see
+    ``gemm_small_m`` (true when this follows ``grouped_gate_up_swiglu`` on the same
+    offsets, as in a mixture layer)."""
     A = act.shape[0]
     per = A / w_down.shape[0]
     if _stream_grouped_applies(act, w_down, A):
@@ -750,7 +756,7 @@ def grouped_down(act: torch.Tensor, offsets: torch.Tensor, w_down: torch.Tensor)
                                    rows_per_pass=8 if per <= 2 else 16)
     if per <= SMALL_M_ROWS_PER_GROUP and _streams_weights(act, w_down):
         return gemm_small_m(act, w_down, None, offsets, False, A,
-                            rows_per_pass=8 if per <= 2 else 16)
+                            rows_per_pass=8 if per <= 2 else 16, offsets_settled=offsets_settled)
     if USE_TCGEN05 and _streams_weights(act, w_down) and w_down.shape[0] <= TCGEN05_MAX_EXPERTS:
         return grouped_gemm_tc(act, offsets, w_down, False)
     return gemm_generic(act, w_down, None, offsets, dual=False, num_out_rows=A)

@@ -114,7 +114,9 @@ class MoeFeedForward:
             x, self.router_w, s.top_k, s.renormalize, s.routed_scale, extra_w=self.shared_gate_w)
         offsets, rows, dest = ops.moe_dispatch(topk_idx, s.num_experts)
         act = ops.grouped_gate_up_swiglu(x, rows, offsets, self.expert_gate_up)
-        y = ops.grouped_down(act, offsets, self.expert_down)
+        # `offsets` was written by the dispatch, two launches back: the down product may
+        # start on its weights while the gate/up product drains
+        y = ops.grouped_down(act, offsets, self.expert_down, offsets_settled=True)
         if side is not None:
             main.wait_stream(side)
         elif self.shared is not None:

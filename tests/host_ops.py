@@ -169,7 +169,7 @@ def grouped_gate_up_swiglu(x, rows, offsets, w_gate_up):
     return out.to(x.dtype)
 
 
-def grouped_down(act, offsets, w_down):
+def grouped_down(act, offsets, w_down, offsets_settled=False):
     E, H, i = w_down.shape
     out = torch.zeros(act.shape[0], H, dtype=torch.float32)
     for e in range(E):
