@@ -100,8 +100,13 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
   for (int i = tid; i < 2 * DT_STAGES * TILE_BYTES / 16; i += DT_THREADS)
     reinterpret_cast<uint4*>(Ks)[i] = make_uint4(0u, 0u, 0u, 0u);
   fence_proxy_async();
-  IX_PDL_WAIT();
+  __syncthreads();     // barriers and zeroes are in place before any copy is issued
 
+  // Lengths and block tables arrive with the step's inputs and the pages hold earlier
+  // steps' keys: all of that was written long before the predecessor in the stream,
+  // which only adds this step's newest key and the query.  So the geometry is worked out
+  // and the first tiles (those that end before the newest key) are requested before the
+  // wait on the predecessor; their latency then overlaps its tail.
   const int split = blockIdx.x, s = blockIdx.z;
   const int rep = heads / kvh;
   const int row_groups = (rep + 15) / 16;
@@ -121,6 +126,49 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
   const int k1 = min(len, k0 + chunk);
   const int n_tiles = k1 > k0 ? (k1 - k0 + DT_BN - 1) / DT_BN : 0;
 
+  // ---- copying warp: lane p brings page p of each tile; the page numbers of the next
+  // tile are fetched before the wait for a free stage, so that their latency is off
+  // the path between "stage free" and "copies issued" ----
+  const int* bt = block_table + (size_t)s * maxb;
+  const int pages_per_tile = DT_BN >> page_shift;
+  const unsigned page_bytes = (unsigned)page_size * HD * 2;
+  auto page_live = [&](int it) {     // does this lane's page of tile `it` hold live keys?
+    const int kp = k0 + it * DT_BN + (lane << page_shift);
+    return lane < pages_per_tile && it < n_tiles && kp + page_size > lo && kp < k1;
+  };
+  auto page_id = [&](int it) {
+    return page_live(it) ? bt[((k0 + it * DT_BN) >> page_shift) + lane] : -1;
+  };
+  auto issue_tile = [&](int it, int pid) {
+    const int stage = it % DT_STAGES;
+    const bool live = page_live(it);
+    const unsigned n_live = __popc(__ballot_sync(0xffffffffu, live));
+    if (lane == 0) mbar_expect_tx(&full_bar[stage], 2u * page_bytes * n_live);
+    __syncwarp();
+    if (live) {
+      const int row = (pid * kvh + kh) << page_shift;
+      unsigned char* kd = Ks + stage * TILE_BYTES;
+      unsigned char* vd = Vs + stage * TILE_BYTES;
+#pragma unroll
+      for (int h = 0; h < HALVES; ++h) {
+        const int off = h * (DT_BN * 128) + (lane << page_shift) * 128;
+        tma_load_2d(kd + off, &map_k, h * 64, row, &full_bar[stage]);
+        tma_load_2d(vd + off, &map_v, h * 64, row, &full_bar[stage]);
+      }
+    }
+  };
+  int issued = 0, pid_next = -1;
+  if (warp == DT_WARPS) {
+    pid_next = page_id(0);
+    while (issued < n_tiles && issued < DT_STAGES && k0 + (issued + 1) * DT_BN <= len - 1) {
+      const int pid = pid_next;
+      pid_next = page_id(issued + 1);
+      issue_tile(issued, pid);
+      ++issued;
+    }
+  }
+  IX_PDL_WAIT();
+
   for (int idx = tid; idx < 16 * CH; idx += DT_THREADS) {
     const int r = idx / CH, c = idx - r * CH;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -138,21 +186,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
   if (warp == DT_WARPS) {
-    // ---- copying warp: lane p brings page p of each tile; the page numbers of the
-    // next tile are fetched before the wait for a free stage, so that their latency
-    // is off the path between "stage free" and "copies issued" ----
-    const int* bt = block_table + (size_t)s * maxb;
-    const int pages_per_tile = DT_BN >> page_shift;
-    const unsigned page_bytes = (unsigned)page_size * HD * 2;
-    auto page_live = [&](int it) {     // does this lane's page of tile `it` hold live keys?
-      const int kp = k0 + it * DT_BN + (lane << page_shift);
-      return lane < pages_per_tile && it < n_tiles && kp + page_size > lo && kp < k1;
-    };
-    auto page_id = [&](int it) {
-      return page_live(it) ? bt[((k0 + it * DT_BN) >> page_shift) + lane] : -1;
-    };
-    int pid_next = page_id(0);
-    for (int it = 0; it < n_tiles; ++it) {
+    for (int it = issued; it < n_tiles; ++it) {
       const int stage = it % DT_STAGES;
       const int pid = pid_next;
       pid_next = page_id(it + 1);
@@ -165,21 +199,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
         }
         break;
       }
-      const bool live = page_live(it);
-      const unsigned n_live = __popc(__ballot_sync(0xffffffffu, live));
-      if (lane == 0) mbar_expect_tx(&full_bar[stage], 2u * page_bytes * n_live);
-      __syncwarp();
-      if (live) {
-        const int row = (pid * kvh + kh) << page_shift;
-        unsigned char* kd = Ks + stage * TILE_BYTES;
-        unsigned char* vd = Vs + stage * TILE_BYTES;
-#pragma unroll
-        for (int h = 0; h < HALVES; ++h) {
-          const int off = h * (DT_BN * 128) + (lane << page_shift) * 128;
-          tma_load_2d(kd + off, &map_k, h * 64, row, &full_bar[stage]);
-          tma_load_2d(vd + off, &map_v, h * 64, row, &full_bar[stage]);
-        }
-      }
+      issue_tile(it, pid);
     }
   } else {
     // ---- computing warps ----
