@@ -17,6 +17,14 @@
 // masked; shared memory is zeroed once so that what a skipped page leaves behind is
 // finite.
 //
+// Contract with the caller when launches carry the programmatic-serialisation
+// attribute: kv_len, the block table and every key and value except the newest of each
+// sequence must have been written before the preceding launch in the stream began; the
+// preceding launch may write the query and the newest key and value only.  (The engine's
+// step does exactly that: lengths and tables arrive with the step's inputs, older keys
+// in earlier steps.)  The kernel uses it to request its first tiles before it waits for
+// the preceding launch.
+//
 // Requires bf16, head_dim 64 or 128, page_size a power of two from 8 to 64.  Every
 // wait on an mbarrier is bounded; a wait that ran out records a code (11: the copying
 // warp, 12: a computing warp) in the caller's status word and the block runs on to its
