@@ -94,7 +94,7 @@ class Executor:
         self.steps_run = 0
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
         self._graphs: Dict[Tuple, _Graph] = {}
-        self._warm = set()
+        self._seen: Dict[Tuple, int] = {}
         self.graph_replays = 0
         self.last_h2d_bytes = 0
 
@@ -235,21 +235,41 @@ class Executor:
         return ctx, rows, lay.R
 
     # ------------------------------------------------------------------
+    # A step's shape: how many tokens each sequence brings (in batch order), the width of
+    # each group's block table (rounded up to a bucket) and the wanted rows.  Steps of
+    # single tokens are captured into a CUDA graph the second time their shape is seen;
+    # other shapes (prompt portions, mixed batches) the third time, and at most
+    # PROMPT_GRAPHS of them are kept (the least recently used goes): prompts rarely
+    # repeat a shape exactly, except for full portions of long prompts and for
+    # benchmarks.
+    PROMPT_GRAPHS = 8
+    SEEN_SHAPES = 4096
+
     def _graph_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         lay = self._layout(entries, bucket_tables=True)
         wanted = tuple(lay.segs[7])
-        key = (lay.S, tuple(lay.widths), wanted)
+        decode = lay.num_decode == lay.S
+        key = (lay.S if decode else tuple(lay.q_lens), tuple(lay.widths), wanted)
         slot = self._graphs.get(key)
-        if slot is None and key not in self._warm:
-            # The first step of a shape runs eagerly: kernels are loaded, attributes set
-            # and the library's plans made outside of any capture.  The second is captured.
-            self._warm.add(key)
-            host = torch.zeros(lay.total, dtype=torch.int32).pin_memory()
-            self._fill(host, lay)
-            dev = host.to(self.device, non_blocking=True)
-            self.last_h2d_bytes = lay.total * 4
-            ctx, rows = self._context(dev, lay, static=True)
-            return self.model.forward(ctx, self.caches, rows)
+        if slot is None:
+            if len(self._seen) >= self.SEEN_SHAPES:
+                self._seen.clear()
+            seen = self._seen[key] = self._seen.get(key, 0) + 1
+            if seen < (2 if decode else 3):
+                # The first step of a shape runs eagerly: kernels are loaded, attributes
+                # set and the library's plans made outside of any capture.
+                host = torch.zeros(lay.total, dtype=torch.int32).pin_memory()
+                self._fill(host, lay)
+                dev = host.to(self.device, non_blocking=True)
+                self.last_h2d_bytes = lay.total * 4
+                ctx, rows = self._context(dev, lay, static=True)
+                return self.model.forward(ctx, self.caches, rows)
+            if not decode:
+                prompts = [k for k in self._graphs if not isinstance(k[0], int)]
+                if len(prompts) >= self.PROMPT_GRAPHS:
+                    del self._graphs[prompts[0]]      # dicts keep insertion order: the oldest
+        elif not decode:
+            self._graphs[key] = self._graphs.pop(key)  # most recently used goes last
         if slot is None:
             host = torch.zeros(lay.total, dtype=torch.int32).pin_memory()
             dev = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
@@ -289,7 +309,7 @@ class Executor:
         self.steps_run += 1
         if self.steps_run % self.ERROR_POLL_STEPS == 0:
             self.poll_errors()
-        if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
+        if self.use_graphs:
             return self._graph_step(entries)
         ctx, rows, _ = self.build_context(entries)
         return self.model.forward(ctx, self.caches, rows)

@@ -38,6 +38,32 @@ def test_long_decoding_with_graphs(tmp_path, dtype, cfg, seed, page):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_prompt_shapes_are_captured_too(tmp_path, dtype):
+    """Six prompts of the same length (and a decoding neighbour from the second one on):
+    from its third occurrence a prompt-carrying shape replays a CUDA graph, and every
+    row still matches the plain model."""
+    cfg = TINY_B
+    d = mc.make_model_dir(cfg, tmp_path / "m", 4,
+                          dtype="float32" if dtype == "float32" else "bfloat16")
+    reqs = mc.make_requests(cfg, [40] * 6 + [12], 7)
+    ref = mc.reference_rows(d, reqs)
+    long = reqs["r6"]
+    steps = [{"step": 0, "entries": [{"id": "r6", "tokens": long[:5], "want": [4]}], "end": []}]
+    for i in range(6):
+        steps.append({"step": i + 1, "entries": [
+            {"id": f"r{i}", "tokens": reqs[f"r{i}"], "want": [0, 39]},
+            {"id": "r6", "tokens": [long[5 + i]], "want": [0]}],
+            "end": [f"r{i}"] + (["r6"] if i == 5 else [])})
+    sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=8, max_live=2,
+                         use_graphs=True)
+    rows = mc.run_trace(sess, steps)
+    assert len(rows) == 1 + 6 * 3
+    ex = sess.executor
+    assert ex.graph_replays >= 4 and any(not isinstance(k[0], int) for k in ex._graphs)
+    mc.compare(rows, ref, mc.bound_for(dtype, d, reqs), f"prompt graphs {dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_of_a_sequence(tmp_path, dtype):
     """Positions 0, 1, 2: one-token prompts, a batch of first tokens, two-token portions."""
     cfg = TINY_B
