@@ -242,7 +242,7 @@ class Executor:
     # PROMPT_GRAPHS of them are kept (the least recently used goes): prompts rarely
     # repeat a shape exactly, except for full portions of long prompts and for
     # benchmarks.
-    PROMPT_GRAPHS = 8
+    PROMPT_GRAPHS = 4
     SEEN_SHAPES = 4096
 
     def _graph_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
