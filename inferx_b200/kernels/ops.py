@@ -432,8 +432,7 @@ def _tma_decode_applies(q, page: int) -> bool:
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                            block_table: torch.Tensor, kv_len: torch.Tensor, max_kv_len: int,
                            window: int, scale: float, splits: Optional[int] = None,
-                           scalar_kernel: bool = False, kernel: Optional[str] = None,
-                           out: Optional[torch.Tensor] = None):
+                           kernel: Optional[str] = None, out: Optional[torch.Tensor] = None):
     """Split-KV attention for a batch in which sequence s brings the one query q[s]
     at position kv_len[s] - 1.  ``kernel`` picks a form ("tma", "mma", "scalar");
     None takes the fastest that applies."""
@@ -452,9 +451,7 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     if kv_len.numel() != S or block_table.shape[0] != S:
         raise KernelError("paged_attention_decode: one query per sequence is required")
     if kernel is None:
-        if scalar_kernel:
-            kernel = "scalar"
-        elif USE_TMA_DECODE and _tma_decode_applies(q, page):
+        if USE_TMA_DECODE and _tma_decode_applies(q, page):
             kernel = "tma"
         else:
             kernel = "mma"
