@@ -1,6 +1,7 @@
-"""Each part alone against the plain function of the same role, and a toy mixer with
-per-request state of its own that is defined here, registered, built from a model
-folder and stepped without any change to the package's files."""
+"""Each part alone against the plain function of the same role, and toy parts defined
+here - a mixer with per-request state of its own, a position encoding with a learned
+table, a feed-forward that routes tokens between two experts - registered, built from
+a model folder and stepped without any change to the package's files."""
 import json
 import math
 import os
@@ -297,3 +298,129 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
     finally:
         unregister_part("mixer", "toy_running_mean")
         arch_registry._ARCHITECTURES.pop("ToyStateForCausalLM", None)
+
+
+# ---------------------------------------------------------------------------
+# another position encoding and a feed-forward with routing, defined in the test
+# ---------------------------------------------------------------------------
+@dataclass(frozen=True)
+class LearnedOffsetSpec:
+    head_dim: int
+    max_positions: int
+    kind: str = "toy_learned_offset"
+
+
+class LearnedOffsetEncoding:
+    """q[t, h, :] += table[pos[t]], k likewise: not a rotation, so it works on dense q
+    and k through ``apply`` and the mixer appends the keys afterwards."""
+
+    def __init__(self, spec, ctx, prefix):
+        self.spec, self.ctx, self.name = spec, ctx, f"{prefix}.position_table"
+
+    def tensors(self):
+        return [TensorDecl(self.name, (self.spec.max_positions, self.spec.head_dim),
+                           keep="float32")]
+
+    def bind(self, w):
+        self.table = w[self.name]
+
+    def rotary_table(self):
+        return None, 0
+
+    def apply(self, q, k, positions):
+        off = self.table[positions.long()]                 # [T, head_dim] fp32
+        q.copy_((q.float() + off[:, None, :]).to(q.dtype))
+        k.copy_((k.float() + off[:, None, :]).to(k.dtype))
+
+
+@dataclass(frozen=True)
+class ParityRoutedSpec:
+    hidden: int
+    kind: str = "toy_parity_routed"
+
+
+class ParityRoutedFeedForward:
+    """Two experts (plain matrices); a token goes to the one its position's parity names.
+    Routing here needs the step's positions, which every feed-forward is handed."""
+
+    def __init__(self, spec, ctx, prefix):
+        self.spec, self.ctx, self.prefix = spec, ctx, prefix
+
+    def tensors(self):
+        h = self.spec.hidden
+        return [TensorDecl(f"{self.prefix}.experts.{e}.weight", (h, h)) for e in range(2)]
+
+    def bind(self, w):
+        self.w = [w[f"{self.prefix}.experts.{e}.weight"] for e in range(2)]
+
+    def forward(self, x, step):
+        odd = (step.positions % 2).bool()
+        out = torch.empty_like(x)
+        out[~odd] = (x[~odd].float() @ self.w[0].float().T).to(x.dtype)
+        out[odd] = (x[odd].float() @ self.w[1].float().T).to(x.dtype)
+        return out
+
+
+def _toy2_spec(cfg):
+    norm = RmsNormSpec(size=cfg.hidden, eps=1e-5)
+    attn = AttentionSpec(hidden=cfg.hidden, heads=3, kv_heads=1, head_dim=16, qkv_bias=True,
+                         scale=0.25, window=6,
+                         position=LearnedOffsetSpec(head_dim=16, max_positions=64))
+    layers = (LayerSpec("model.layers.0", norm, attn, norm, ParityRoutedSpec(cfg.hidden)),)
+    return ModelSpec(architecture="ToyRoutedForCausalLM", vocab_size=cfg.vocab, hidden=cfg.hidden,
+                     layers=layers, schedule=(RunEntry(0),), final_norm=norm, tied_head=False)
+
+
+def _toy2_plain(w, tokens, hidden):
+    x = w["model.embed_tokens.weight"][torch.tensor(tokens)]
+    T = len(tokens)
+    p = "model.layers.0.self_attn"
+    n = plain.rmsnorm(x, w["model.layers.0.input_layernorm.weight"], 1e-5)
+    off = w[f"{p}.position_table"][:T]
+    q = (n @ w[f"{p}.q_proj.weight"].T + w[f"{p}.q_proj.bias"]).view(T, 3, 16) + off[:, None, :]
+    k = (n @ w[f"{p}.k_proj.weight"].T + w[f"{p}.k_proj.bias"]).view(T, 1, 16) + off[:, None, :]
+    v = (n @ w[f"{p}.v_proj.weight"].T + w[f"{p}.v_proj.bias"]).view(T, 1, 16)
+    o = plain.attention(q, k, v, 0.25, 6)
+    x = x + o.reshape(T, 48) @ w[f"{p}.o_proj.weight"].T
+    n = plain.rmsnorm(x, w["model.layers.0.post_attention_layernorm.weight"], 1e-5)
+    y = torch.empty_like(n)
+    for t in range(T):
+        y[t] = w[f"model.layers.0.mlp.experts.{t % 2}.weight"] @ n[t]
+    x = x + y
+    n = plain.rmsnorm(x, w["model.norm.weight"], 1e-5)
+    return n @ w["lm_head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_position_encoding_and_routed_feed_forward(tmp_path, dtype):
+    register_part("position", "toy_learned_offset", LearnedOffsetEncoding)
+    register_part("feed_forward", "toy_parity_routed", ParityRoutedFeedForward)
+    register_architecture(
+        "ToyRoutedForCausalLM",
+        lambda obj, where: SimpleNamespace(hidden=obj["hidden_size"], vocab=obj["vocab_size"],
+                                           eos_token_ids=()),
+        _toy2_spec)
+    try:
+        cfg = {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": 40, "vocab_size": 61,
+               "torch_dtype": "float32"}
+        d = str(tmp_path / "toy2")
+        write_random_model(cfg, d, seed=8, std=0.2,
+                           dtype="float32" if dtype == "float32" else "bfloat16")
+        _, w = plain.read_model_folder(d)
+        assert "model.layers.0.self_attn.position_table" in w
+        assert "model.layers.0.mlp.experts.1.weight" in w and "lm_head.weight" in w
+        reqs = mc.make_requests({"vocab_size": 61}, [11, 40, 3, 26], 5)
+        ref = {}
+        for rid, toks in reqs.items():
+            lg = _toy2_plain(w, toks, 40)
+            for p in range(len(toks)):
+                ref[(rid, p)] = lg[p]
+        for kind in ("whole", "tail", "portions", "mixed"):
+            steps = mc.TRACE_KINDS[kind](reqs)
+            sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=4, max_live=4)
+            rows = mc.run_trace(sess, steps)
+            mc.compare(rows, ref, 2e-5 if dtype == "float32" else 4e-2, f"toy2/{kind}/{dtype}")
+    finally:
+        unregister_part("position", "toy_learned_offset")
+        unregister_part("feed_forward", "toy_parity_routed")
+        arch_registry._ARCHITECTURES.pop("ToyRoutedForCausalLM", None)
