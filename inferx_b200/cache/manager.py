@@ -19,6 +19,7 @@ executor only reads it.
 """
 from __future__ import annotations
 
+from array import array
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -71,7 +72,7 @@ class CacheGroup:
 class _Request:
     slot: int
     length: int = 0                                  # tokens whose keys/values are in the cache
-    tables: List[List[int]] = field(default_factory=list)   # per group: page id per page index
+    tables: List["array"] = field(default_factory=list)     # per group: page id per page index
     first_live: List[int] = field(default_factory=list)     # per group: first page index still held
 
 
@@ -115,7 +116,7 @@ class CacheManager:
             return None
         slot = self._free_slots.pop()
         self._fresh_slots.append(slot)
-        self._requests[rid] = _Request(slot=slot, tables=[[] for _ in self.groups],
+        self._requests[rid] = _Request(slot=slot, tables=[array("i") for _ in self.groups],
                                        first_live=[0 for _ in self.groups])
         return slot
 
@@ -147,7 +148,9 @@ class CacheManager:
     def slot(self, rid) -> int:
         return self._req(rid).slot
 
-    def table(self, rid, group: int) -> List[int]:
+    def table(self, rid, group: int) -> "array":
+        """The request's block table in this group: an ``array('i')`` of page ids (it
+        reads like a list and hands its memory to numpy without a copy)."""
         return self._req(rid).tables[group]
 
     def capacity(self, rid) -> int:

@@ -27,6 +27,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
@@ -57,18 +58,27 @@ def _bucket(n: int) -> int:
     return b
 
 
+# order of the index arrays inside a step's staging buffer
+_TOKENS, _POSITIONS, _SEQ_OF_TOKEN, _CU_Q, _Q_POS0, _KV_LEN, _STATE_SLOT, _LOGIT_ROWS, \
+    _CU_Q_PROMPT = range(9)
+_FIXED_SEGS = 9        # then, per cache group: slots, block table
+
+
 @dataclass
 class _Layout:
-    """Host-side description of one batch, ready to be copied to the device."""
+    """Host-side description of one batch: every index array of the step laid out in one
+    int32 buffer (``buf``), with the offset and length of each."""
     T: int
     S: int
     R: int
-    segs: List[List[int]]
+    buf: "np.ndarray"
     offs: List[int]
+    lens: List[int]
     total: int
     widths: List[int]          # block-table width per group
     q_lens: List[int]
     kv_lens: List[int]
+    wanted: Tuple[int, ...]
     num_decode: int = 0        # sequences with a single token; they come first
 
 
@@ -100,28 +110,21 @@ class Executor:
 
     # ------------------------------------------------------------------
     def _layout(self, entries: Sequence[StepEntry], bucket_tables: bool) -> _Layout:
-        """Validate the batch and lay its index arrays out as lists."""
+        """Validate the batch and lay its index arrays out in one int32 buffer."""
         mgr = self.manager
         if not entries:
             raise StepError("a step needs at least one entry")
-        seen = set()
-        token_ids: List[int] = []
-        positions: List[int] = []
-        seq_of_token: List[int] = []
-        cu_q = [0]
-        q_pos0: List[int] = []
-        kv_len: List[int] = []
-        state_slot: List[int] = []
-        logit_rows: List[int] = []
         n_groups = len(mgr.groups)
-        slots: List[List[int]] = [[] for _ in range(n_groups)]
         ps = mgr.page_size
         vocab = self.vocab
         # single tokens first, prompt portions after them, each kind in the order given:
         # attention can then treat the two parts of a mixed batch as two plain batches
         order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)
-        base_of = [0] * len(entries)
-        for s, i in enumerate(order):
+        S = len(entries)
+        seen = set()
+        starts: List[int] = []
+        q_lens: List[int] = []
+        for i in order:
             e = entries[i]
             rid = e.request
             if rid in seen:
@@ -137,90 +140,123 @@ class Executor:
                 raise StepError(
                     f"request {rid!r}: positions {start}..{start + n - 1} exceed the "
                     f"{mgr.capacity(rid)} tokens its pages hold (reserve first)")
-            base_of[i] = len(token_ids)
-            for tok in e.tokens:
-                tok = int(tok)
-                if not (0 <= tok < vocab):
-                    raise StepError(f"request {rid!r}: token id {tok} is outside the "
-                                    f"vocabulary of {vocab}")
-                token_ids.append(tok)
             for w in e.want:
                 if not (0 <= int(w) < n):
                     raise StepError(f"request {rid!r}: wanted place {int(w)} is not among "
                                     f"its {n} tokens")
-            for g in range(n_groups):
-                table = mgr.table(rid, g)
-                sl = slots[g]
-                for p in range(start, start + n):
-                    page = table[p // ps]
-                    if page < 0:
-                        raise StepError(f"request {rid!r}: the page of position {p} was "
-                                        "given back")
-                    sl.append(page * ps + p % ps)
-            positions.extend(range(start, start + n))
-            seq_of_token.extend([s] * n)
-            cu_q.append(cu_q[-1] + n)
-            q_pos0.append(start)
-            kv_len.append(start + n)
-            state_slot.append(mgr.slot(rid))
-        for i, e in enumerate(entries):      # logits come back in the order of the entries
-            logit_rows.extend(base_of[i] + int(w) for w in e.want)
-        num_decode = sum(1 for e in entries if len(e.tokens) == 1)
-        cu_q_prompt = [c - cu_q[num_decode] for c in cu_q[num_decode:]]
-        widths, tables = [], []
+            starts.append(start)
+            q_lens.append(n)
+        T = sum(q_lens)
+        R = sum(len(e.want) for e in entries)
+        num_decode = sum(1 for n in q_lens if n == 1)
+        tables = [[mgr.table(entries[i].request, g) for i in order] for g in range(n_groups)]
+        widths = []
         for g in range(n_groups):
-            rows = [mgr.table(entries[i].request, g) for i in order]
-            mb = max(1, max(len(r) for r in rows))
-            if bucket_tables:
-                mb = _bucket(mb)
-            flat: List[int] = []
-            for r in rows:
-                flat.extend(r)
-                flat.extend([-1] * (mb - len(r)))
-            widths.append(mb)
-            tables.append(flat)
-        segs = [token_ids, positions, seq_of_token, cu_q, q_pos0, kv_len, state_slot, logit_rows]
+            mb = max(1, max(len(r) for r in tables[g]))
+            widths.append(_bucket(mb) if bucket_tables else mb)
+        lens = [T, T, T, S + 1, S, S, S, R, S - num_decode + 1]
         for g in range(n_groups):
-            segs += [slots[g], tables[g]]
-        segs.append(cu_q_prompt)
+            lens += [T, S * widths[g]]
         offs, total = [], 0
-        for sgm in segs:
+        for n in lens:
             offs.append(total)
-            total += _pad4(len(sgm))
-        S = len(entries)
-        return _Layout(T=len(token_ids), S=S, R=len(logit_rows), segs=segs, offs=offs,
-                       total=max(total, 4), widths=widths,
-                       q_lens=[cu_q[i + 1] - cu_q[i] for i in range(S)], kv_lens=kv_len,
-                       num_decode=num_decode)
+            total += _pad4(n)
+        total = max(total, 4)
+        buf = np.zeros(total, dtype=np.int32)
+
+        def seg(k):
+            return buf[offs[k]:offs[k] + lens[k]]
+
+        tok, pos, seq_of = seg(_TOKENS), seg(_POSITIONS), seg(_SEQ_OF_TOKEN)
+        cu_q, q_pos0, kv_len, state_slot = seg(_CU_Q), seg(_Q_POS0), seg(_KV_LEN), seg(_STATE_SLOT)
+        slot_segs = [seg(_FIXED_SEGS + 2 * g) for g in range(n_groups)]
+        base_of = [0] * S
+        base = 0
+        for s, i in enumerate(order):
+            e = entries[i]
+            rid, n, start = e.request, q_lens[s], starts[s]
+            base_of[i] = base
+            if n == 1:
+                t = int(e.tokens[0])
+                if not (0 <= t < vocab):
+                    raise StepError(f"request {rid!r}: token id {t} is outside the "
+                                    f"vocabulary of {vocab}")
+                tok[base] = t
+                pos[base] = start
+                seq_of[base] = s
+                for g in range(n_groups):
+                    page = tables[g][s][start // ps]
+                    if page < 0:
+                        raise StepError(f"request {rid!r}: the page of position {start} was "
+                                        "given back")
+                    slot_segs[g][base] = page * ps + start % ps
+            else:
+                ids = np.asarray(e.tokens, dtype=np.int64)
+                if ids.min() < 0 or ids.max() >= vocab:
+                    bad = int(ids[(ids < 0) | (ids >= vocab)][0])
+                    raise StepError(f"request {rid!r}: token id {bad} is outside the "
+                                    f"vocabulary of {vocab}")
+                tok[base:base + n] = ids
+                p = np.arange(start, start + n, dtype=np.int64)
+                pos[base:base + n] = p
+                seq_of[base:base + n] = s
+                for g in range(n_groups):
+                    row = np.frombuffer(tables[g][s], dtype=np.int32)
+                    pages = row[p // ps].astype(np.int64)
+                    if pages.min() < 0:
+                        gone = int(p[pages < 0][0])
+                        raise StepError(f"request {rid!r}: the page of position {gone} was "
+                                        "given back")
+                    slot_segs[g][base:base + n] = pages * ps + p % ps
+            cu_q[s + 1] = base + n
+            q_pos0[s] = start
+            kv_len[s] = start + n
+            state_slot[s] = mgr.slot(rid)
+            base += n
+        wanted: List[int] = []
+        for i, e in enumerate(entries):      # logits come back in the order of the entries
+            wanted.extend(base_of[i] + int(w) for w in e.want)
+        if R:
+            seg(_LOGIT_ROWS)[:] = wanted
+        seg(_CU_Q_PROMPT)[:] = cu_q[num_decode:] - cu_q[num_decode]
+        for g in range(n_groups):
+            mb = widths[g]
+            view = seg(_FIXED_SEGS + 2 * g + 1).reshape(S, mb)
+            view.fill(-1)
+            for s, row in enumerate(tables[g]):
+                if len(row):
+                    view[s, :len(row)] = np.frombuffer(row, dtype=np.int32)
+        return _Layout(T=T, S=S, R=R, buf=buf, offs=offs, lens=lens, total=total, widths=widths,
+                       q_lens=q_lens, kv_lens=[a + n for a, n in zip(starts, q_lens)],
+                       wanted=tuple(wanted), num_decode=num_decode)
 
     @staticmethod
     def _fill(host: torch.Tensor, lay: _Layout) -> None:
-        for o, sgm in zip(lay.offs, lay.segs):
-            if sgm:
-                host[o:o + len(sgm)] = torch.tensor(sgm, dtype=torch.int32)
+        host.numpy()[:lay.total] = lay.buf
 
     def _context(self, dev: torch.Tensor, lay: _Layout, static: bool):
         mgr = self.manager
 
         def seg(i):
-            return dev[lay.offs[i]:lay.offs[i] + len(lay.segs[i])]
+            return dev[lay.offs[i]:lay.offs[i] + lay.lens[i]]
 
         groups = []
         for g, grp in enumerate(mgr.groups):
-            groups.append(GroupView(block_table=seg(9 + 2 * g).view(lay.S, lay.widths[g]),
-                                    slots=seg(8 + 2 * g), page_size=mgr.page_size,
-                                    window=grp.window))
+            groups.append(GroupView(
+                block_table=seg(_FIXED_SEGS + 2 * g + 1).view(lay.S, lay.widths[g]),
+                slots=seg(_FIXED_SEGS + 2 * g), page_size=mgr.page_size, window=grp.window))
         max_kv = max(lay.kv_lens)
         if static:   # a captured graph must hold for every length its table width allows
             max_kv = max(w for w in lay.widths) * mgr.page_size if lay.widths else max_kv
         ctx = StepContext(
-            num_tokens=lay.T, num_seqs=lay.S, token_ids=seg(0), positions=seg(1),
-            seq_of_token=seg(2), cu_q=seg(3), q_pos0=seg(4), kv_len=seg(5), state_slot=seg(6),
+            num_tokens=lay.T, num_seqs=lay.S, token_ids=seg(_TOKENS), positions=seg(_POSITIONS),
+            seq_of_token=seg(_SEQ_OF_TOKEN), cu_q=seg(_CU_Q), q_pos0=seg(_Q_POS0),
+            kv_len=seg(_KV_LEN), state_slot=seg(_STATE_SLOT),
             groups=groups, max_q_len=max(lay.q_lens), max_kv_len=max_kv,
             q_lens=list(lay.q_lens), kv_lens=list(lay.kv_lens),
             all_decode=all(n == 1 for n in lay.q_lens), num_decode_seqs=lay.num_decode,
-            cu_q_prompt=seg(8 + 2 * len(mgr.groups)))
-        return ctx, (seg(7) if lay.R else None)
+            cu_q_prompt=seg(_CU_Q_PROMPT))
+        return ctx, (seg(_LOGIT_ROWS) if lay.R else None)
 
     def build_context(self, entries: Sequence[StepEntry]):
         """(StepContext, logit_rows tensor or None, number of wanted rows) for an eager step."""
@@ -247,7 +283,7 @@ class Executor:
 
     def _graph_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         lay = self._layout(entries, bucket_tables=True)
-        wanted = tuple(lay.segs[7])
+        wanted = lay.wanted
         decode = lay.num_decode == lay.S
         key = (lay.S if decode else tuple(lay.q_lens), tuple(lay.widths), wanted)
         slot = self._graphs.get(key)
