@@ -1,9 +1,10 @@
 """Kernel-level timings with achieved bandwidth or FLOP rate.
 
-    python -m inferx_b200.kernels.microbench attn_decode --batch 8 --context 4096
+    python -m inferx_b200.kernels.microbench attn_decode --batch 8 --context 4096 [--form tma|mma|scalar]
     python -m inferx_b200.kernels.microbench grouped --tokens 8
     python -m inferx_b200.kernels.microbench dense --rows 8 --n 6144 --k 2048
-    python -m inferx_b200.kernels.microbench attn_prefill --tokens 2048
+    python -m inferx_b200.kernels.microbench attn_prefill --tokens 2048 [--form tc|mma]
+    python -m inferx_b200.kernels.microbench router --tokens 2048
     python -m inferx_b200.kernels.microbench grouped --tokens 2048
 
 Each case runs one kernel face at Qwen1.5-MoE-A2.7B sizes (or the sizes given),
