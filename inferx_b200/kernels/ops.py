@@ -20,6 +20,11 @@ import torch
 
 from . import library
 
+# The library GEMM behind ``torch.mm`` may add its split-K partial sums in bf16; sums are
+# to be fp32 here (a small result of large terms otherwise carries the rounding of the
+# terms).  A process-wide torch setting: this package turns it off where it is imported.
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
 F32, BF16 = 0, 1
 
 _ERRORS = {
@@ -98,9 +103,13 @@ def _count(n: int = 1):
 
 
 # Steps of at most this many tokens launch their kernels with programmatic stream
-# serialisation.  Measured at the benchmark's layer sizes: batch 8 and 32 gain (2.5 % at
-# 32), batch 64 loses 9 %.
-DEPENDENT_LAUNCH_MAX_TOKENS = 32
+# serialisation, and their dense projections stream the weights with this library's own
+# kernel (SMALL_M_DENSE_ROWS below is the same number on purpose).  Beyond it the dense
+# projections go to the library GEMM and dependent launch is off: a step that mixes
+# dependent launches with the library's plain launches measured far slower than either
+# (batch 32: 11.7 ms mixed, 9.8 ms own kernels + dependent launch, 9.2 ms library GEMMs
+# without it; batch 16: 7.3 / 5.9 / 6.0 ms).
+DEPENDENT_LAUNCH_MAX_TOKENS = 16
 
 
 def set_dependent_launch(on: bool) -> None:
@@ -590,7 +599,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 USE_TCGEN05 = True           # prompt-sized grouped products go to the tcgen05 kernel
 TCGEN05_MAX_EXPERTS = 1024   # its per-expert tile prefix lives in shared memory
 SMALL_M_ROWS_PER_GROUP = 8   # grouped: up to this many rows per expert on average
-SMALL_M_DENSE_ROWS = 32      # dense: up to this many rows stream the weights once
+SMALL_M_DENSE_ROWS = 16      # dense: up to this many rows stream the weights once
 
 
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor],

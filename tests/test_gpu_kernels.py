@@ -482,6 +482,13 @@ def test_small_m_dense(M, N, K):
     out32 = ops.linear(x.cuda(), w.cuda(), out_dtype=torch.float32)
     torch.testing.assert_close(out32.cpu(), host_ops.linear(x, w, torch.float32),
                                rtol=1e-3, atol=1e-3)
+    if K % 8 == 0:
+        # the streaming kernel itself, whatever ``linear`` chose for this row count
+        per_pass = 8 if M <= 8 else (16 if M <= 16 else 32)
+        direct = ops.gemm_small_m(x.cuda(), w.cuda().unsqueeze(0), None, None, False, M,
+                                  rows_per_pass=per_pass)
+        torch.testing.assert_close(direct.cpu().float(), host_ops.linear(x, w).float(),
+                                   **_tol(dtype))
     if N % 2 == 0:
         act = ops.gate_up_swiglu(x.cuda(), w.cuda())
         torch.testing.assert_close(act.cpu().float(), host_ops.gate_up_swiglu(x, w).float(),
