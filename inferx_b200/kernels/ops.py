@@ -598,7 +598,10 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
 USE_TCGEN05 = True           # prompt-sized grouped products go to the tcgen05 kernel
 TCGEN05_MAX_EXPERTS = 1024   # its per-expert tile prefix lives in shared memory
-SMALL_M_ROWS_PER_GROUP = 8   # grouped: up to this many rows per expert on average
+# grouped: up to this many rows per expert on average stream the weights with the
+# mma.sync kernel; beyond, the persistent tcgen05 kernel is faster (measured crossover at
+# 60 experts: between 24 and 32 tokens of top-4 routing)
+SMALL_M_ROWS_PER_GROUP = 2
 SMALL_M_DENSE_ROWS = 16      # dense: up to this many rows stream the weights once
 
 
