@@ -567,8 +567,32 @@ static int decode_splits(int S, int heads, int kvh, int max_kv_len, int per_sm) 
   const int rep = heads / (kvh > 0 ? kvh : 1);
   const long long base = (long long)S * kvh * ((rep + 15) / 16);
   const int slots = 148 * per_sm;
-  long long splits = base >= slots ? 1 : slots / base;
   const int max_by_len = (max_kv_len + 127) / 128;   // at least two 64-key tiles per block
+  long long splits;
+  if (base < slots) {
+    splits = slots / base;
+  } else {
+    // More blocks than one wave holds.  A last wave that fills at least half of the
+    // places still saturates the memory system and simply ends sooner; a thinner one
+    // runs as long as a half-full one would (320 blocks on 296 places: the last 24 cost
+    // as much as 148).  Splitting the keys a few ways evens that out and pays for the
+    // merge it adds: take the count, up to four, with the least such waste, charging two
+    // per cent for each extra split.
+    splits = 1;
+    double best = 0.0;
+    for (int s = 1; s <= 4; ++s) {
+      const long long blocks = base * s;
+      const long long full = blocks / slots;
+      const double rest = (double)(blocks - full * slots) / (double)slots;
+      const double ideal = (double)full + rest;
+      const double cost = (double)full + (rest > 0.0 ? (rest < 0.5 ? 0.5 : rest) : 0.0);
+      const double score = ideal / cost * (1.0 - 0.02 * (s - 1));
+      if (score > best + 1e-9) {
+        best = score;
+        splits = s;
+      }
+    }
+  }
   if (splits > max_by_len) splits = max_by_len;
   if (splits > 64) splits = 64;
   if (splits < 1) splits = 1;
