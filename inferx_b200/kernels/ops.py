@@ -325,6 +325,12 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     return out
 
 
+# below this many tokens the router runs as two kernels (logits by one warp per (token,
+# expert), then selection); from it on as one fused kernel (equal at 128 tokens, 13 us
+# against 19-21 us at 200-256)
+ROUTER_FEW_TOKENS = 128
+
+
 def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, renormalize: bool, scale: float,
                 extra_w: Optional[torch.Tensor] = None
                 ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
@@ -344,7 +350,7 @@ def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, renormalize: bool,
     tw = torch.empty((T, top_k), dtype=torch.float32, device=x.device)
     ti = torch.empty((T, top_k), dtype=torch.int32, device=x.device)
     ex = torch.empty((T,), dtype=torch.float32, device=x.device) if extra_w is not None else None
-    few = T < 2 * 148   # few tokens: logits by many blocks, then a selection kernel
+    few = T < ROUTER_FEW_TOKENS   # few tokens: logits by many blocks, then a selection kernel
     scratch = torch.empty((T, E), dtype=torch.float32, device=x.device) if few else None
     code = _lib().ix_router_topk(_ptr(x), _ptr(w), _ptr(extra_w), _dtype_code(x), T, H, E, top_k,
                                  1 if renormalize else 0, ctypes.c_float(scale), _ptr(tw),
