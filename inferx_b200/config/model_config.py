@@ -221,7 +221,6 @@ class Qwen2MoeConfig:
         for i in self.mlp_only_layers:
             need(0 <= i < self.num_hidden_layers, f"mlp_only_layers entry {i} is not a layer")
         sparse = [self.layer_is_sparse(i) for i in range(self.num_hidden_layers)]
-        need(any(sparse), "no layer is sparse: check decoder_sparse_step / mlp_only_layers")
         if not all(sparse):
             need(self.intermediate_size > 0,
                  "'intermediate_size' is required because some layers are dense")

@@ -42,6 +42,12 @@ def test_per_layer_choices_follow_the_config(tiny_a, tiny_b):
     assert b.layers[0].mixer.position.theta == 1e6 and b.layers[0].input_norm.eps == 1e-5
 
 
+def test_a_model_may_have_dense_layers_only(tiny_a):
+    _, spec = config_from_json(dict(tiny_a, mlp_only_layers=[0, 1], intermediate_size=48))
+    assert [l.ffn.kind for l in spec.layers] == ["swiglu", "swiglu"]
+    assert spec.layers[0].ffn.intermediate == 48
+
+
 @pytest.mark.parametrize("change,match", [
     ({"num_experts_per_tok": 8}, "exceeds num_experts"),
     ({"num_experts_per_tok": None}, "num_experts_per_tok"),
@@ -51,7 +57,6 @@ def test_per_layer_choices_follow_the_config(tiny_a, tiny_b):
     ({"norm_topk_prob": 1}, "true or false"),
     ({"vocab_size": None}, "required key 'vocab_size'"),
     ({"decoder_sparse_step": 0}, "at least 1"),
-    ({"mlp_only_layers": [0, 1]}, "no layer is sparse"),
     ({"mlp_only_layers": [0]}, "intermediate_size"),
     ({"mlp_only_layers": [7]}, "not a layer"),
     ({"use_sliding_window": True}, "sliding_window"),
