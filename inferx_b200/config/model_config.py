@@ -157,10 +157,30 @@ class Qwen2MoeConfig:
         else:
             attn_bias = True
         dtype = r.string("torch_dtype", r.string("dtype", "bfloat16"))
-        if "rope_scaling" in obj and obj["rope_scaling"] is not None:
-            # only YaRN exists in the reference, and not for this architecture
-            # (src/model/config.cc:461-506)
-            raise ConfigError(f"{where}: 'rope_scaling' is not supported for {name}")
+        # rotary constants: 'rope_theta' at the top level, or inside 'rope_parameters'
+        # (the newer spelling of the same file).  Any scaling of the angles is refused:
+        # only YaRN exists in the reference, and not for this architecture
+        # (src/model/config.cc:461-506).
+        rope_theta_default: Any = 10000.0
+        for key in ("rope_scaling", "rope_parameters"):
+            sub = obj.get(key)
+            if sub is None:
+                continue
+            if not isinstance(sub, Mapping):
+                raise ConfigError(f"{where}: '{key}' must be an object or null, got {sub!r}")
+            kind = sub.get("rope_type", sub.get("type", "default"))
+            if kind != "default":
+                raise ConfigError(
+                    f"{where}: '{key}' of type {kind!r} is not supported for {name} "
+                    f"(plain rotary embedding only)")
+            if "rope_theta" in sub:
+                rope_theta_default = _Reader(sub, f"{where}: {key}").number("rope_theta")
+        # the feed-forwards are SwiGLU (src/backends/cuda/ops/layers.cu:512-529); another
+        # activation would be computed wrongly, so it is refused
+        act = obj.get("hidden_act", "silu")
+        if act != "silu":
+            raise ConfigError(f"{where}: 'hidden_act' {act!r} is not supported for {name} "
+                              f"(only 'silu')")
         cfg = cls(
             vocab_size=r.integer("vocab_size"),
             hidden_size=hidden,
@@ -170,7 +190,7 @@ class Qwen2MoeConfig:
             head_dim=head_dim,
             intermediate_size=r.integer("intermediate_size", inter_default),
             rms_norm_eps=r.number("rms_norm_eps", 1e-6),
-            rope_theta=r.number("rope_theta", 10000.0),
+            rope_theta=r.number("rope_theta", rope_theta_default),
             tie_word_embeddings=r.boolean("tie_word_embeddings", False),
             attention_bias=attn_bias,
             num_experts=num_experts,

@@ -42,6 +42,15 @@ def test_per_layer_choices_follow_the_config(tiny_a, tiny_b):
     assert b.layers[0].mixer.position.theta == 1e6 and b.layers[0].input_norm.eps == 1e-5
 
 
+def test_rotary_base_in_either_spelling(tiny_a):
+    cfg = dict(tiny_a)
+    cfg.pop("rope_theta", None)
+    cfg["rope_parameters"] = {"rope_type": "default", "rope_theta": 12345.0}
+    assert config_from_json(cfg)[0].rope_theta == 12345.0
+    assert config_from_json(dict(tiny_a, rope_scaling=None, hidden_act="silu"))[0].rope_theta \
+        == tiny_a["rope_theta"]
+
+
 def test_a_model_may_have_dense_layers_only(tiny_a):
     _, spec = config_from_json(dict(tiny_a, mlp_only_layers=[0, 1], intermediate_size=48))
     assert [l.ffn.kind for l in spec.layers] == ["swiglu", "swiglu"]
@@ -61,6 +70,8 @@ def test_a_model_may_have_dense_layers_only(tiny_a):
     ({"mlp_only_layers": [7]}, "not a layer"),
     ({"use_sliding_window": True}, "sliding_window"),
     ({"rope_scaling": {"type": "yarn"}}, "rope_scaling"),
+    ({"rope_parameters": {"rope_type": "linear", "factor": 2.0}}, "rope_parameters"),
+    ({"hidden_act": "gelu"}, "hidden_act"),
     ({"torch_dtype": "int8"}, "torch_dtype"),
     ({"architectures": ["Qwen2MoeForCausalLM", "X"]}, "exactly one"),
 ])
