@@ -43,6 +43,18 @@ A27B = {
 FULL_LAYERS = 24
 METRIC = "decode tok/s at batch 8, context 4096 (Qwen1.5-MoE-A2.7B sizes)"
 
+# The larger configuration of the same architecture (about 115 GB of bf16 weights);
+# `--sizes 57b-a14b` measures it: decode at context 32768, and a 2,048-token prompt
+# portion beside the decoding requests in one step.
+Q57B = dict(A27B, num_hidden_layers=28, hidden_size=3584, num_attention_heads=28,
+            num_key_value_heads=4, num_experts=64, num_experts_per_tok=8,
+            moe_intermediate_size=2560, shared_expert_intermediate_size=20480,
+            intermediate_size=18944)
+SIZES = {
+    "a2.7b": {"cfg": A27B, "name": "Qwen1.5-MoE-A2.7B sizes", "context": 4096, "big_batch": 64},
+    "57b-a14b": {"cfg": Q57B, "name": "Qwen2-57B-A14B sizes", "context": 32768, "big_batch": 32},
+}
+
 
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -145,7 +157,7 @@ def prefill_flops(cfg, T):
     return L * (per_tok * T + attn) + 2 * cfg["vocab_size"] * H
 
 
-def make_runtime(cfg, batch, context, extra_tokens, use_graphs=True):
+def make_runtime(cfg, batch, context, extra_tokens, use_graphs=True, max_slots=None):
     import torch
     from inferx_b200.engine import Runtime, load_model
     from inferx_b200.weights.loader import RandomSource
@@ -153,7 +165,7 @@ def make_runtime(cfg, batch, context, extra_tokens, use_graphs=True):
                           source=RandomSource(0, device="cuda"))
     page = 16
     pages = batch * (-(-(context + extra_tokens) // page) + 1)
-    rt = Runtime(model, page_size=page, num_pages=pages, max_slots=max(batch, 1),
+    rt = Runtime(model, page_size=page, num_pages=pages, max_slots=max_slots or max(batch, 1),
                  use_graphs=use_graphs)
     return rt
 
@@ -267,6 +279,40 @@ def time_prefill(rt, tokens, reps, warmup):
         rt.executor.step([StepEntry("p", toks, [tokens - 1])])
         e.record()
         torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(s.elapsed_time(e))
+    mgr.close("p")
+    times.sort()
+    return times[len(times) // 2]
+
+
+def time_mixed(rt, batch, context, chunk, reps, warmup):
+    """One step that carries a prompt portion of ``chunk`` tokens beside ``batch``
+    decoding requests at ``context``: milliseconds a step (median)."""
+    import torch
+    from inferx_b200.engine import StepEntry
+    fill_context(rt, batch, context)
+    mgr = rt.manager
+    g = torch.Generator().manual_seed(9)
+    toks = torch.randint(0, rt.vocab_size, (chunk,), generator=g).tolist()
+    times = []
+    for i in range(warmup + reps):
+        if mgr.has("p"):
+            mgr.close("p")
+        mgr.open("p")
+        assert mgr.reserve("p", chunk)
+        for r in range(batch):
+            assert mgr.reserve(r, mgr.length(r) + 1)
+        entries = [StepEntry(r, [7 + r], [0]) for r in range(batch)]
+        entries.append(StepEntry("p", toks, [chunk - 1]))
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        rt.executor.step(entries)
+        e.record()
+        torch.cuda.synchronize()
+        for r in range(batch):
+            mgr.advance(r, 1)
         if i >= warmup:
             times.append(s.elapsed_time(e))
     mgr.close("p")
@@ -450,8 +496,10 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--context", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--sizes", default="a2.7b", choices=sorted(SIZES),
+                    help="layer sizes: the headline configuration, or the 57B one")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the default decode run")
     ap.add_argument("--no-graphs", action="store_true")
@@ -478,10 +526,36 @@ def main(argv=None):
     if args.serving:
         return serving(args)
     hbm_peak, tf_peak, peak_src = peaks()
-    cfg = dict(A27B, num_hidden_layers=args.layers)
+    sizes = SIZES[args.sizes]
+    full_layers = sizes["cfg"]["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = full_layers
+    if args.context is None:
+        args.context = sizes["context"]
+    cfg = dict(sizes["cfg"], num_hidden_layers=args.layers)
     B, C = args.batch, args.context
-    max_b = B if (args.skip_points or args.breakdown) else max(B, 64)
-    rt = make_runtime(cfg, max_b, C, args.steps + args.warmup + 8, use_graphs=not args.no_graphs)
+    big_b, big_c = sizes["big_batch"], C
+    extra = args.steps + args.warmup + 8
+    points_wanted = not (args.skip_points or args.breakdown)
+    # what the device has to hold: weights, and the cache pool of the widest run (plus
+    # the 2,048-token portion of the mixed step); the widest run's context is cut, in
+    # steps of 4096, until it fits
+    wb = weight_bytes(cfg)
+    weights = wb["layers"] * (wb["per_layer_fixed"] + cfg["num_experts"] * wb["per_expert"]) \
+        + 2 * wb["head"]
+    kv_tok = 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2 * args.layers
+    room = 0.88 * torch.cuda.get_device_properties(0).total_memory - weights - (6 << 30)
+    pool_tokens = B * (C + extra + 16) + 2048 + 64
+    if points_wanted:
+        while big_c > 4096 and big_b * (big_c + extra + 16) * kv_tok > room:
+            big_c -= 4096
+        pool_tokens = max(pool_tokens, big_b * (big_c + extra + 16))
+    if pool_tokens * kv_tok > room:
+        print(f"bench.py: {weights / 1e9:.1f} GB of weights and {pool_tokens * kv_tok / 1e9:.1f} GB "
+              f"of cache do not fit this device; give fewer --layers or a shorter --context")
+        return 2
+    rt = make_runtime(cfg, 1, pool_tokens, 0, use_graphs=not args.no_graphs,
+                      max_slots=max(B, big_b if points_wanted else B) + 1)
 
     if args.breakdown:
         print(breakdown(rt, B, C, min(args.steps, 4),
@@ -493,14 +567,16 @@ def main(argv=None):
     step_bytes = decode_step_bytes(cfg, B, C, touched)
     achieved = step_bytes / (dec["ms_per_step"] / 1e3) / 1e9
     out = {
-        "metric": METRIC, "value": round(dec["tok_s"], 1), "unit": "tok/s", "n_gpus": 1,
+        "metric": METRIC if args.sizes == "a2.7b" else
+        f"decode tok/s at batch {B}, context {C} ({sizes['name']})",
+        "value": round(dec["tok_s"], 1), "unit": "tok/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dec["ms_per_step"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), uniform random token ids, random cache",
         "impl": "ours",
         "config": {
-            "model": "Qwen1.5-MoE-A2.7B sizes", "global_batch": B, "seq_len": C,
-            "parallelism": "single GPU", "layers": args.layers, "layers_of_config": FULL_LAYERS,
+            "model": sizes["name"], "global_batch": B, "seq_len": C,
+            "parallelism": "single GPU", "layers": args.layers, "layers_of_config": full_layers,
             "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
             "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "experts": cfg["num_experts"], "top_k": cfg["num_experts_per_tok"],
@@ -520,10 +596,15 @@ def main(argv=None):
     }
     points = {}
     if not args.skip_points:
-        for b in (1, 64):
-            d = time_decode(rt, b, C, max(8, args.steps // 2), args.warmup)
+        for b, c in ((1, C), (big_b, big_c)):
+            d = time_decode(rt, b, c, max(8, args.steps // 2), args.warmup)
             points[f"decode_b{b}"] = round(d["tok_s"], 1)
             points[f"decode_b{b}_ms"] = round(d["ms_per_step"], 4)
+            if c != C:
+                points[f"decode_b{b}_context"] = c
+        mms = time_mixed(rt, B, C, 2048, reps=5, warmup=3)
+        points["mixed_2048_plus_decode_ms"] = round(mms, 3)
+        points["mixed_2048_plus_decode_tok_s"] = round((2048 + B) / (mms / 1e3), 1)
         pms = time_prefill(rt, 2048, reps=5, warmup=3)
         fl = prefill_flops(cfg, 2048)
         out["prefill"] = {"value": round(2048 / (pms / 1e3), 1), "tokens": 2048,
@@ -533,8 +614,11 @@ def main(argv=None):
         out["points"] = points
     del rt
     torch.cuda.empty_cache()
-    if not args.skip_points:
+    if not args.skip_points and args.sizes == "a2.7b":
         out["e2e"] = time_e2e(cfg, B, C, args.steps, args.warmup)
+    elif not args.skip_points:
+        out["e2e"] = {"unmeasured": "a second copy of the weights for the entry point's own "
+                                    "engine is not made at these sizes"}
     print(json.dumps(out))
     return 0
 
