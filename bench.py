@@ -2,16 +2,20 @@
 """Decode and prefill throughput at Qwen1.5-MoE-A2.7B sizes on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096]
-                    [--layers L] [--impl reference]
+                    [--layers L] [--sizes a2.7b|57b-a14b] [--impl reference]
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second of the default run:
 random weights at the A2.7B layer sizes, batch 8, context 4096, bfloat16, timed on
 the device with CUDA events over exactly K decode steps after W warm-up steps.
 ``e2e`` is the same through ``Engine.step`` (host token ids in through pinned
 memory, sampled ids back to the host every step).  ``prefill`` is one 2,048-token
-prompt in one step; ``points`` holds decode at batch 1 and 64; ``roofline`` is the
+prompt in one step; ``points`` holds decode at batch 1 and 64 and one step that
+carries a 2,048-token prompt portion beside the decoding requests; ``roofline`` is the
 bytes a decode step has to read (every weight it uses once, and the cache of the
 live requests) over its time, against the measured copy bandwidth.
+
+``--sizes 57b-a14b`` runs the same measurements at the Qwen2-57B-A14B layer sizes
+(context 32768, the wide point at batch 32 and the longest context that fits).
 
 A decode step's working set (gigabytes of weights and cache) is far larger than the
 126 MB L2, so nothing stays resident between timed iterations.
