@@ -19,7 +19,7 @@
 // 128-row tile of an expert's weights is read once for up to 256 of its tokens.
 //
 // The unit of work is, for one expert, 128 output features (gate and up rows when
-// DUAL: two accumulators) for a tile of up to BT (256 or 128) of the expert's tokens;
+// DUAL: two accumulators) for a tile of up to BT (128 to 256) of the expert's tokens;
 // an expert with more rows is cut into equal tiles.
 // The kernel is persistent: one block per SM takes work items round robin, ordered so
 // that the feature tiles of one token tile run at the same time on neighbouring SMs
@@ -30,8 +30,9 @@
 // per instruction, bf16 in, fp32 accumulate in TMEM) and releases stages with
 // tcgen05.commit; warps 2-5 read the finished accumulator with tcgen05.ld (a thread
 // holds one feature for 32 tokens), apply the epilogue and store bf16.  Where tensor
-// memory has room for two accumulator sets, the epilogue of one item overlaps the MMAs
-// of the next.  Token rows of the last box beyond the tile, feature rows beyond N and
+// memory has room for two accumulator sets (plain form; SwiGLU form at 128 tokens), the
+// epilogue of one item overlaps the MMAs of the next; where it has not, the epilogue is
+// short enough (branch-free, a microsecond or two a tile) that the wider tile still pays.  Token rows of the last box beyond the tile, feature rows beyond N and
 // the K tail are computed on whatever TMA delivered (neighbouring rows or zero fill)
 // and never stored.
 //
@@ -50,7 +51,7 @@
 #define TC_BK 64
 #define TC_THREADS 192
 #define TC_W_BYTES (TC_BF * TC_BK * 2)   // 16 KB: one 128 x 64 bf16 weight tile
-#define TC_SMEM_STAGES (192 * 1024)      // shared memory given to the ring of stages
+#define TC_SMEM_STAGES (208 * 1024)      // shared memory given to the ring of stages
 #define TC_MAX_EXPERTS 1024              // the per-expert tile prefix lives in shared memory
 
 enum { TC_ERR_PRODUCER = 1, TC_ERR_MMA = 2, TC_ERR_EPILOGUE = 3 };
@@ -272,16 +273,24 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
-        // a warp's 32 threads hold 32 neighbouring features of one token: 64-byte stores
-        bf16* dst = out + (size_t)(it.m0 + c0) * N + f;
+        // All 32 values are computed without a branch (columns past the tile hold
+        // whatever the MMA made of the rows TMA delivered; they are not stored), so the
+        // exponentials and reciprocals of different columns overlap; a branch per column
+        // would serialise their latencies.  The fast reciprocal's error is far below a
+        // bf16 ulp.
+        bf16 r[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          if (f_ok && c0 + i < it.n_valid) {
-            float a = g[i];
-            if (DUAL) a = a / (1.0f + __expf(-a)) * u[i];
-            dst[(size_t)i * N] = __float2bfloat16_rn(a);
-          }
+          float a = g[i];
+          if (DUAL) a = __fdividef(a, 1.0f + __expf(-a)) * u[i];
+          r[i] = __float2bfloat16_rn(a);
         }
+        // a warp's 32 threads hold 32 neighbouring features of one token: 64-byte stores
+        bf16* dst = out + (size_t)(it.m0 + c0) * N + f;
+        const int n_here = f_ok ? it.n_valid - c0 : 0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < n_here) dst[(size_t)i * N] = r[i];
       }
       ++n_done;
     }
@@ -358,15 +367,25 @@ IX_API int ix_grouped_gemm_tc(const void* a, const int* offsets, const void* w, 
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) & 15) return IX_ERR_ALIGN;
   const long long w_rows = dual ? 2LL * N : N;
   if ((long long)E * w_rows > 0x7fffffffLL) return IX_ERR_SIZE;
-  // SwiGLU form: 128-token tiles always, since two accumulator sets of that width fit
-  // in tensor memory and the epilogue (exp, divide) of one item then overlaps the next
-  // item's MMAs; with 160- or 256-token tiles (one set) it cannot, and that cost more
-  // than reading the weights a second time out of L2 (183 and 187 us against 164 us at
-  // 2048 tokens).  Plain form: 256-token tiles (each weight tile read once) unless
-  // experts have so few rows that the narrow tile's deeper ring wins.
-  if (dual)
-    return launch_tc<true, 128>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream);
-  if (A_rows / E <= 96)
-    return launch_tc<false, 128>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream);
-  return launch_tc<false, 256>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream);
+  // Width of the token tile: the mean rows of an expert plus 15 % for imbalance, cut
+  // into as few tiles as 256 rows allow, and then the narrowest of 128 / 160 / 192 / 256
+  // that holds such a tile.  The narrower the tile, the smaller its stage and the more
+  // stages the ring holds; what the kernel achieves follows the bytes in flight, not the
+  // tensor pipe (measured at 60 experts of 1408 x 2048: SwiGLU form, 136 rows an expert:
+  // 150 / 153 / 154 us at 160 / 128 / 256; 273 rows: 223 / 237 / 243 us; plain form, 136
+  // rows: 76 / 98 / 79 us; 102 rows: 69 us at 128 against 71-74 us).
+  const double rows = 1.15 * (double)A_rows / (double)E;
+  const int cuts = rows <= 256.0 ? 1 : (int)((rows + 255.0) / 256.0);
+  const double per = rows / cuts;
+  const int bt = per <= 128.0 ? 128 : per <= 160.0 ? 160 : per <= 192.0 ? 192 : 256;
+#define IX_TC(D)                                                                              \
+  do {                                                                                        \
+    if (bt == 128) return launch_tc<D, 128>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream); \
+    if (bt == 160) return launch_tc<D, 160>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream); \
+    if (bt == 192) return launch_tc<D, 192>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream); \
+    return launch_tc<D, 256>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream);   \
+  } while (0)
+  if (dual) IX_TC(true);
+  IX_TC(false);
+#undef IX_TC
 }

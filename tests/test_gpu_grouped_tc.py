@@ -23,6 +23,8 @@ def _routing(T, E, k, seed):
     (1000, 128, 128, 4, 1),     # about 250 rows per expert: one wide tile each
     (2000, 128, 136, 3, 1),     # several token tiles per expert
     (64, 2048, 1408, 6, 4),     # the bench's widths
+    (330, 128, 136, 2, 1),      # about 165 rows per expert: the 192-token tile
+    (480, 192, 72, 7, 2),       # about 137 rows per expert: the 160-token tile, some experts cut in two
 ])
 def test_grouped_gemm_tc(T, H, I, E, k):
     from inferx_b200.kernels import ops
