@@ -479,7 +479,8 @@ def serving(args):
         "prompt_tokens": sum(lens), "generated_tokens": st["tokens_generated"],
         "seconds": round(dt, 3), "output_tok_s": round(st["tokens_generated"] / dt, 1),
         "total_tok_s": round((st["tokens_generated"] + st["tokens_prefilled"]) / dt, 1),
-        "steps": st["steps"], "preemptions": st["preemptions"],
+        "steps": st["steps"], "graph_replays": st["graph_replays"],
+        "preemptions": st["preemptions"],
         "tokens_prefilled_incl_recompute": st["tokens_prefilled"],
         "pool_pages": pages, "pool_fraction_of_demand": args.pool_fraction,
         "finish_reasons": reasons, "layers": layers, "layers_of_config": FULL_LAYERS}))
@@ -527,15 +528,15 @@ def main(argv=None):
     import torch
     from inferx_b200.kernels import ops
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
-    if args.serving:
-        return serving(args)
-    hbm_peak, tf_peak, peak_src = peaks()
     sizes = SIZES[args.sizes]
     full_layers = sizes["cfg"]["num_hidden_layers"]
     if args.layers is None:
         args.layers = full_layers
     if args.context is None:
         args.context = sizes["context"]
+    if args.serving:
+        return serving(args)
+    hbm_peak, tf_peak, peak_src = peaks()
     cfg = dict(sizes["cfg"], num_hidden_layers=args.layers)
     B, C = args.batch, args.context
     big_b, big_c = sizes["big_batch"], C

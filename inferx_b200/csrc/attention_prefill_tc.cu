@@ -25,7 +25,10 @@
 // P within bf16's range.
 //
 // Two blocks fit on an SM (96 KB of shared memory and 256 columns of tensor memory
-// each), so one block's softmax overlaps the other's MMAs.  Every mbarrier wait is
+// each), so one block's softmax overlaps the other's MMAs.  A step with few (query
+// tile, head) items over a long context (a prompt portion late in its sequence) has its
+// keys cut into runs, one block each (blockIdx.z), that leave their unnormalised O,
+// reference max and sum for a small merge kernel.  Every mbarrier wait is
 // bounded; a wait that ran out records a code (21: copies, 22: MMA, 23: softmax) in
 // the caller's status word and the block runs to its end (its output is then not
 // meaningful).
@@ -92,7 +95,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const int* __restrict__ block_table, const int* __restrict__ cu_q,
                        const int* __restrict__ q_pos0, bf16* __restrict__ out, int S, int heads,
                        int kvh, int page_size, int page_shift, int maxb, int window,
-                       float scale_log2e, int* __restrict__ status) {
+                       float scale_log2e, int* __restrict__ status, int nsplit,
+                       float* __restrict__ part_o, float* __restrict__ part_ml) {
   constexpr int HALVES = HD / 64;
   constexpr int Q_BYTES = FA_BM * HD * 2;
   constexpr int Q_HALF = FA_BM * 128;
@@ -137,8 +141,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int pmax = pos0 + rows_valid - 1;
   const int kv_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
   const int kv_hi = pmax + 1;
-  const int kt0 = kv_lo & ~(FA_BN - 1);
-  const int n_tiles = (kv_hi - kt0 + FA_BN - 1) / FA_BN;
+  // the tile's keys, cut into nsplit runs of whole 64-key tiles (blockIdx.z takes one)
+  const int kt_first = kv_lo & ~(FA_BN - 1);
+  const int n_all = (kv_hi - kt_first + FA_BN - 1) / FA_BN;
+  const int per_split = (n_all + nsplit - 1) / nsplit;
+  const int kt0 = kt_first + (int)blockIdx.z * per_split * FA_BN;
+  const int n_tiles = max(0, min(per_split, n_all - (int)blockIdx.z * per_split));
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   if ((smem_u32(smem) & 1023u) != 0) {           // the swizzle needs it; never seen
@@ -365,6 +373,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_done, (n_tiles - 1) & 1, abortp));
     if (!ok) {
       if (lane == 0 && !*abortp) { atomicExch(status, FA_ERR_SOFTMAX); *abortp = 1; }
+    } else if (nsplit > 1) {
+      // this run's share: O and the sum as they stand against the reference max, for
+      // the merge kernel (a run without keys for a row leaves max = -inf, which the
+      // merge skips)
+      if (n_tiles > 0) tc_fence_after();
+      const size_t hrow = (size_t)(tok0 + q0 + row) * heads + h;
+      float* po = part_o + (hrow * nsplit + blockIdx.z) * HD;
+      const bool live = n_tiles > 0 && l_run > 0.f;
+      if (n_tiles > 0) {
+#pragma unroll
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          float o[32];
+          tc_ld32(lane_addr + c0, o);            // every lane takes part in the load
+          if (row < rows_valid && live) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<float4*>(po + c0 + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+          }
+        }
+      }
+      if (row < rows_valid) {
+        part_ml[(hrow * nsplit + blockIdx.z) * 2] = live ? m_ref : -INFINITY;
+        part_ml[(hrow * nsplit + blockIdx.z) * 2 + 1] = live ? l_run : 0.f;
+      }
     } else if (n_tiles > 0) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
@@ -408,11 +440,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   }
 }
 
+// Merge of the runs' shares: out = sum_j o_j 2^(m_j - M) / sum_j l_j 2^(m_j - M), one
+// block per (query, head).
+__global__ void attn_prefill_tc_merge_kernel(const float* __restrict__ part_o,
+                                             const float* __restrict__ part_ml,
+                                             bf16* __restrict__ out, int hd, int nsplit) {
+  const size_t hrow = blockIdx.x;
+  const float* ml = part_ml + hrow * nsplit * 2;
+  float M = -INFINITY;
+  for (int j = 0; j < nsplit; ++j) M = fmaxf(M, ml[2 * j]);
+  float L = 0.f;
+  for (int j = 0; j < nsplit; ++j)
+    if (ml[2 * j] != -INFINITY) L += ml[2 * j + 1] * fa_exp2(ml[2 * j] - M);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float o = 0.f;
+    for (int j = 0; j < nsplit; ++j)
+      if (ml[2 * j] != -INFINITY)
+        o += part_o[(hrow * nsplit + j) * hd + d] * fa_exp2(ml[2 * j] - M);
+    out[hrow * hd + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+  }
+}
+
 template <int HD>
 static int launch_prefill_tc(const void* q, const void* kc, const void* vc, long long cache_rows,
                              const int* bt, const int* cu_q, const int* q_pos0, void* out, int T,
                              int S, int heads, int kvh, int page_size, int page_shift, int maxb,
-                             int window, float scale, int* status, cudaStream_t stream) {
+                             int window, float scale, int* status, int nsplit, float* part_o,
+                             float* part_ml, cudaStream_t stream) {
   CUtensorMap map_q, map_k, map_v;
   int rc = ix_tensor_map_bf16_2d(&map_q, q, T, (long long)heads * HD, 64, FA_BM);
   if (rc != IX_OK) return rc;
@@ -426,30 +480,56 @@ static int launch_prefill_tc(const void* q, const void* kc, const void* vc, long
   if (e != cudaSuccess) return (int)e;
   const int tiles = (T + FA_BM - 1) / FA_BM + S;   // every sequence can add one partial tile
   if (tiles > 65535) return IX_ERR_SIZE;
-  dim3 grid(heads, tiles);
+  dim3 grid(heads, tiles, nsplit);
   kern<<<grid, FA_THREADS, smem, stream>>>(map_q, map_k, map_v, bt, cu_q, q_pos0, (bf16*)out, S,
                                            heads, kvh, page_size, page_shift, maxb, window,
-                                           scale * 1.4426950408889634f, status);
+                                           scale * 1.4426950408889634f, status, nsplit, part_o,
+                                           part_ml);
+  rc = ix_launch_status();
+  if (rc != IX_OK || nsplit == 1) return rc;
+  attn_prefill_tc_merge_kernel<<<T * heads, HD >= 128 ? 128 : 64, 0, stream>>>(
+      part_o, part_ml, (bf16*)out, HD, nsplit);
   return ix_launch_status();
 }
 
+// Runs to cut every query tile's keys into: only when the step has so few (query tile,
+// head) items that they leave SMs idle (a short prompt portion over a long context),
+// and never runs shorter than 2,048 keys (the merge is a launch and a pass over fp32
+// partial outputs of its own; measured at 16 heads of 128: 512 queries over 8,192 keys
+// 129 -> 55 us, over 32,768 keys 506 -> 160 us, 128 queries over 8,192 keys 123 -> 31 us
+// with more and shorter runs).  `keys` bounds the longest context of the step.
+IX_API int ix_attn_prefill_tc_splits(int T, int S, int heads, int keys, int window) {
+  if (T <= 0 || S <= 0 || heads <= 0 || keys <= 0) return 1;
+  const long long items = (long long)heads * ((T + FA_BM - 1) / FA_BM + S - 1);
+  long long k = keys;
+  if (window > 0 && k > (long long)window + FA_BM + FA_BN) k = window + FA_BM + FA_BN;
+  const long long by_items = (2 * 148) / (items > 0 ? items : 1);
+  const long long by_keys = k / (32 * FA_BN);
+  long long n = by_items < by_keys ? by_items : by_keys;
+  if (n > 16) n = 16;
+  return n < 1 ? 1 : (int)n;
+}
+
 // q: [T, heads, hd] bf16; caches [num_pages, kvh, page_size, hd] bf16; status: one int
-// in device memory, zero before the first call.
+// in device memory, zero before the first call.  splits > 1: part_o [T, heads, splits,
+// hd] and part_ml [T, heads, splits, 2] fp32 scratch.
 IX_API int ix_paged_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache,
                                          int num_pages, const int* block_table, const int* cu_q,
                                          const int* q_pos0, void* out, int T, int S, int heads,
                                          int kvh, int hd, int page_size, int max_blocks,
-                                         int window, float scale, int* status,
-                                         cudaStream_t stream) {
+                                         int window, float scale, int splits, float* part_o,
+                                         float* part_ml, int* status, cudaStream_t stream) {
   if (T <= 0 || S <= 0) return IX_OK;
   if (heads <= 0 || kvh <= 0 || heads % kvh != 0 || max_blocks <= 0 || window < 0 ||
       num_pages <= 0 || status == nullptr)
     return IX_ERR_SIZE;
   if (heads > 65535) return IX_ERR_SIZE;
+  if (splits < 1 || splits > 64 || (splits > 1 && (!part_o || !part_ml))) return IX_ERR_SIZE;
   if (!(hd == 64 || hd == 128) ||
       !(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64))
     return IX_ERR_UNSUPPORTED;
-  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out |
+       (uintptr_t)part_o) & 15)
     return IX_ERR_ALIGN;
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
@@ -458,8 +538,8 @@ IX_API int ix_paged_attention_prefill_tc(const void* q, const void* k_cache, con
   if (hd == 128)
     return launch_prefill_tc<128>(q, k_cache, v_cache, cache_rows, block_table, cu_q, q_pos0, out,
                                   T, S, heads, kvh, page_size, page_shift, max_blocks, window,
-                                  scale, status, stream);
+                                  scale, status, splits, part_o, part_ml, stream);
   return launch_prefill_tc<64>(q, k_cache, v_cache, cache_rows, block_table, cu_q, q_pos0, out, T,
                                S, heads, kvh, page_size, page_shift, max_blocks, window, scale,
-                               status, stream);
+                               status, splits, part_o, part_ml, stream);
 }

@@ -194,6 +194,7 @@ class Engine:
             "preemptions": self.scheduler.preemptions,
             "tokens_generated": self.tokens_generated,
             "tokens_prefilled": self.tokens_prefilled,
+            "graph_replays": self.runtime.executor.graph_replays,
             "running": len(self.scheduler.running),
             "waiting": len(self.scheduler.waiting),
             "pages_free": [p.free_count for p in mgr.pools],

@@ -280,6 +280,8 @@ class Executor:
     # benchmarks.
     PROMPT_GRAPHS = 4
     SEEN_SHAPES = 4096
+    DECODE_SEEN = 2       # a shape is captured when it is seen this many times
+    PROMPT_SEEN = 3
 
     def _graph_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         lay = self._layout(entries, bucket_tables=True)
@@ -291,7 +293,7 @@ class Executor:
             if len(self._seen) >= self.SEEN_SHAPES:
                 self._seen.clear()
             seen = self._seen[key] = self._seen.get(key, 0) + 1
-            if seen < (2 if decode else 3):
+            if seen < (self.DECODE_SEEN if decode else self.PROMPT_SEEN):
                 # The first step of a shape runs eagerly: kernels are loaded, attributes
                 # set and the library's plans made outside of any capture.
                 host = torch.zeros(lay.total, dtype=torch.int32).pin_memory()

@@ -4,6 +4,7 @@
     python -m inferx_b200.kernels.microbench grouped --tokens 8
     python -m inferx_b200.kernels.microbench dense --rows 8 --n 6144 --k 2048
     python -m inferx_b200.kernels.microbench attn_prefill --tokens 2048 [--form tc|mma]
+    python -m inferx_b200.kernels.microbench attn_prefill --tokens 512 --context 8192 [--splits N]
     python -m inferx_b200.kernels.microbench router --tokens 2048
     python -m inferx_b200.kernels.microbench grouped --tokens 2048
 
@@ -163,7 +164,8 @@ def attn_prefill(args):
     from . import ops
     T, heads, kvh, hd, page = args.tokens, args.heads, args.kv_heads, args.head_dim, args.page
     dt = torch.bfloat16
-    pages = -(-T // page)
+    C = max(args.context if args.context_given else T, T)   # keys: the portion ends the context
+    pages = -(-C // page)
     kc = torch.randn(pages, kvh, page, hd, device="cuda", dtype=dt)
     vc = torch.randn(pages, kvh, page, hd, device="cuda", dtype=dt)
     bt = torch.randperm(pages, device="cuda").to(torch.int32).view(1, pages)
@@ -172,17 +174,18 @@ def attn_prefill(args):
         seq_of_token=torch.zeros(T, dtype=torch.int32, device="cuda"),
         positions=torch.arange(T, dtype=torch.int32, device="cuda"),
         cu_q=torch.tensor([0, T], dtype=torch.int32, device="cuda"),
-        q_pos0=torch.zeros(1, dtype=torch.int32, device="cuda"),
-        kv_len=torch.full((1,), T, dtype=torch.int32, device="cuda"),
-        max_q_len=T, max_kv_len=T, all_decode=False, num_seqs=1, num_tokens=T)
+        q_pos0=torch.full((1,), C - T, dtype=torch.int32, device="cuda"),
+        kv_len=torch.full((1,), C, dtype=torch.int32, device="cuda"),
+        max_q_len=T, max_kv_len=C, all_decode=False, num_seqs=1, num_tokens=T)
     scale = 1.0 / math.sqrt(hd)
 
     def fn(i):
         ops.paged_attention_prefill(q, kc, vc, bt, step.cu_q, step.q_pos0, args.window, scale,
-                                    kernel=args.form or None)
+                                    kernel=args.form or None, splits=args.splits or None)
     us = _time(fn, 1, args.iters)
-    flops = 4 * heads * hd * T * T / 2
-    return {"case": "attn_prefill", "tokens": T, "heads": heads, "head_dim": hd,
+    flops = 4 * heads * hd * (T * T / 2 + T * (C - T))
+    return {"case": "attn_prefill", "tokens": T, "context": C, "heads": heads, "head_dim": hd,
+            "splits": args.splits or "auto",
             "form": args.form or "auto",
             "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
 
@@ -211,6 +214,7 @@ def main(argv=None):
     ap.add_argument("--swiglu", action="store_true")
     ap.add_argument("--eager", action="store_true", help="plain launches, no graph capture")
     args = ap.parse_args(argv)
+    args.context_given = any(a == "--context" or a.startswith("--context=") for a in (argv or sys.argv[1:]))
     if not torch.cuda.is_available():
         print("microbench needs a CUDA device", file=sys.stderr)
         return 3

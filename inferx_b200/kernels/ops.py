@@ -523,10 +523,15 @@ def _tc_prefill_applies(q, page: int) -> bool:
 def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                             block_table: torch.Tensor, cu_q: torch.Tensor, q_pos0: torch.Tensor,
                             window: int, scale: float, kernel: Optional[str] = None,
-                            out: Optional[torch.Tensor] = None):
+                            out: Optional[torch.Tensor] = None, splits: Optional[int] = None,
+                            max_kv_len: Optional[int] = None):
     """Tensor-core attention for a ragged batch: sequence s brings the queries
     q[cu_q[s]:cu_q[s+1]] at positions q_pos0[s], q_pos0[s]+1, ...  ``kernel`` picks a
-    form ("tc", "mma"); None takes the fastest that applies."""
+    form ("tc", "mma"); None takes the fastest that applies.  ``splits`` (tcgen05 form):
+    runs the keys of a query tile are cut into, merged afterwards; None lets the kernel
+    module choose (more than one only for few queries over a long context, which it
+    judges from ``max_kv_len``, the longest context of the step, or else from the width
+    of the block table)."""
     _chk("q", q, torch.bfloat16)
     _chk("k_cache", k_cache, q.dtype)
     _chk("v_cache", v_cache, q.dtype)
@@ -557,18 +562,30 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         _chk("out", out, q.dtype)
         if out.shape != q.shape:
             raise KernelError("paged_attention_prefill: out must have the query's shape")
+    launches = 1
     if kernel == "tc":
+        if splits is None:
+            keys = int(max_kv_len) if max_kv_len else block_table.shape[1] * page
+            splits = _lib().ix_attn_prefill_tc_splits(T, S, heads, keys, window)
+        if not 1 <= splits <= 64:
+            raise KernelError(f"paged_attention_prefill: splits must be 1..64, got {splits}")
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = torch.empty((T, heads, splits, hd), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((T, heads, splits, 2), dtype=torch.float32, device=q.device)
+            launches = 2
         code = _lib().ix_paged_attention_prefill_tc(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), P, _ptr(block_table), _ptr(cu_q),
             _ptr(q_pos0), _ptr(out), T, S, heads, kvh, hd, page, block_table.shape[1], window,
-            ctypes.c_float(scale), _ptr(_tc_status(q.device)), _stream())
+            ctypes.c_float(scale), splits, _ptr(part_o), _ptr(part_ml),
+            _ptr(_tc_status(q.device)), _stream())
     else:
         code = _lib().ix_paged_attention_prefill(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(cu_q), _ptr(q_pos0),
             _ptr(out), _dtype_code(q), T, S, heads, kvh, hd, page, block_table.shape[1], window,
             ctypes.c_float(scale), _stream())
     _check(code, "paged_attention_prefill")
-    _count()
+    _count(launches)
     return out
 
 
@@ -594,10 +611,10 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                                    step.max_kv_len, window, scale, out=out[:nd])
             paged_attention_prefill(q[nd:], k_cache, v_cache, block_table[nd:],
                                     step.cu_q_prompt, step.q_pos0[nd:], window, scale,
-                                    out=out[nd:])
+                                    out=out[nd:], max_kv_len=step.max_kv_len)
             return out
         return paged_attention_prefill(q, k_cache, v_cache, block_table, step.cu_q, step.q_pos0,
-                                       window, scale)
+                                       window, scale, max_kv_len=step.max_kv_len)
     return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,
                                    step.positions, window, scale)
 

@@ -541,6 +541,42 @@ def test_paged_attention_prefill(heads, kvh, hd, page, window):
                                           q_pos0.cuda(), window, scale, kernel=form)
         torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2,
                                    msg=lambda m: f"{form}: {m}")
+    if "tc" in _prefill_forms(page):
+        # the keys of every query tile cut into runs (some of them empty, some wholly
+        # masked for the earlier queries of the tile) and merged
+        for splits in (2, 3, 7):
+            out = ops.paged_attention_prefill(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(),
+                                              cu_q.cuda(), q_pos0.cuda(), window, scale,
+                                              kernel="tc", splits=splits)
+            torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2,
+                                       msg=lambda m: f"tc, {splits} runs: {m}")
+    ops.check_async_errors()
+
+
+def test_short_portion_over_a_long_context_is_cut_into_runs():
+    """70 queries at the end of 5,000 keys: few (query tile, head) items, so the tcgen05
+    form cuts the keys into runs by itself (two launches); one far key is marked so that
+    a run that was dropped or merged with the wrong weight shows."""
+    ops = _ops()
+    heads, kvh, hd, page = 4, 2, 128, 16
+    n, ql = 5000, 70
+    q, kc, vc, bt, seq_of, pos = _paged_case(torch.bfloat16, heads, kvh, hd, page, 0, [n], [ql],
+                                             seed=11)
+    far = 1234
+    kc[bt[0, far // page], :, far % page] *= 3.0
+    cu_q = torch.tensor([0, ql], dtype=torch.int32)
+    q_pos0 = torch.tensor([n - ql], dtype=torch.int32)
+    scale = 1.0 / math.sqrt(hd)
+    ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, 0, scale)
+    assert ops._lib().ix_attn_prefill_tc_splits(ql, 1, heads, n, 0) > 1
+    before = ops.LAUNCHES[0]
+    out = ops.paged_attention_prefill(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cu_q.cuda(),
+                                      q_pos0.cuda(), 0, scale, kernel="tc")
+    assert ops.LAUNCHES[0] - before == 2
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+    one = ops.paged_attention_prefill(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cu_q.cuda(),
+                                      q_pos0.cuda(), 0, scale, kernel="tc", splits=1)
+    torch.testing.assert_close(one.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
     ops.check_async_errors()
 
 
