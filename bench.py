@@ -24,7 +24,6 @@ from __future__ import annotations
 
 import argparse
 import json
-import math
 import os
 import subprocess
 import sys
@@ -236,7 +235,6 @@ def count_step_kernels(rt, batch, context):
     import torch
     from inferx_b200.engine import StepEntry
     from inferx_b200.kernels import ops
-    from inferx_b200.parts.feed_forward import MoeFeedForward
     fill_context(rt, batch, context)
     mgr = rt.manager
     seen = []

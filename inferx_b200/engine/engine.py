@@ -12,7 +12,6 @@ less than one sequence of ``max_model_len``.
 """
 from __future__ import annotations
 
-import time
 from dataclasses import dataclass, field
 from typing import Any, Dict, Hashable, Iterator, List, Mapping, Optional, Sequence
 

@@ -18,9 +18,8 @@ from __future__ import annotations
 import json
 import os
 import sys
-from typing import Any, Dict, Iterable, List, Mapping, Optional
+from typing import Any, Iterable, Mapping, Optional
 
-import numpy as np
 import torch
 
 from .executor import StepEntry

@@ -8,7 +8,6 @@ function.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Any, Mapping, Optional, Sequence, Union
 
 import torch

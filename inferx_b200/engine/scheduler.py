@@ -31,8 +31,8 @@ ids, exactly the split of the reference (include/inferx/scheduler/scheduler.h:
 from __future__ import annotations
 
 import collections
-from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional, Sequence
+from dataclasses import dataclass
+from typing import Deque, Hashable, List, Optional, Sequence
 
 from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams

@@ -12,13 +12,13 @@ src/model/qwen2.cc:1066).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import List, Optional
 
 import torch
 
 from ..weights import loader as wl
 from ..weights.loader import TensorDecl
-from .base import BuildContext, LayerCache, PagedKvNeed, StateNeed, StepContext
+from .base import BuildContext, LayerCache, StepContext
 from .registry import build_part
 
 

@@ -14,7 +14,7 @@ here, only a registration of the class that runs them (``parts/registry.py``).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Optional
 
 

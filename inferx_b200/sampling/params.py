@@ -4,7 +4,7 @@ min-p, stop tokens, ``ignore_eos`` and the seed are honoured; penalties, minimum
 tokens and log-probabilities are accepted only at their neutral values."""
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Tuple
 
 

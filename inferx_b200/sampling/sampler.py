@@ -8,7 +8,7 @@ skips the parameter upload.
 """
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import Sequence
 
 import torch
 
