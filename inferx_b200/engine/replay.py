@@ -57,6 +57,8 @@ class ReplaySession:
         mgr = self.manager
         for e in step.get("entries", []):
             rid, tokens = e["id"], list(e["tokens"])
+            if not tokens:
+                continue                  # an entry that brings nothing runs nothing
             if not mgr.has(rid):
                 if mgr.open(rid) is None:
                     raise ReplayError(f"step {step.get('step')}: no free state slot for "
@@ -122,5 +124,6 @@ def main(argv=None) -> int:
         sys.stdout.write(f"done {step}\n")
         sys.stdout.flush()
 
-    run_stream(session, sys.stdin, args.out, report)
+    # one line at a time: the sender may wait for "done <step>" before it writes the next
+    run_stream(session, iter(sys.stdin.readline, ""), args.out, report)
     return 0

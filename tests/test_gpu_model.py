@@ -71,6 +71,36 @@ def test_trace_run_program(tmp_path, dtype):
     mc.compare(rows, ref, mc.bound_for(dtype, d, reqs), f"trace_run/{dtype}")
 
 
+def test_trace_run_answers_step_by_step(tmp_path):
+    """The sender writes one step, waits for its 'done' line, then writes the next;
+    the files of earlier steps are complete by then."""
+    cfg = TINY_A
+    d = mc.make_model_dir(cfg, tmp_path / "m", 2, dtype="bfloat16")
+    reqs = mc.make_requests(cfg, [21, 8], 2)
+    steps = traces.portions(reqs)
+    out = tmp_path / "out"
+    p = subprocess.Popen(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype",
+         "float32", "--out", str(out), "--max-tokens", str(traces.peak_tokens(steps))],
+        stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, bufsize=1)
+    try:
+        for s in steps:
+            if s is steps[0]:        # an entry without tokens runs nothing and holds nothing
+                s = dict(s, entries=s["entries"] + [{"id": "idle", "tokens": [], "want": []}])
+            p.stdin.write(json.dumps(s) + "\n")
+            p.stdin.flush()
+            assert p.stdout.readline().strip() == f"done {s['step']}"
+            n = sum(len(e["want"]) for e in s["entries"])
+            if n:
+                got = np.fromfile(out / f"{s['step']}.f32", dtype="<f4")
+                assert got.size == n * cfg["vocab_size"] and np.isfinite(got).all()
+        p.stdin.close()
+        assert p.wait(timeout=120) == 0, p.stderr.read()[-2000:]
+    finally:
+        if p.poll() is None:
+            p.kill()
+
+
 MID = {
     "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
     "num_hidden_layers": 2, "hidden_size": 2048, "num_attention_heads": 16,
