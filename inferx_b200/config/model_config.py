@@ -7,14 +7,19 @@ include/inferx/support/json.h:51-69), required sizes, defaults for optional
 keys, and validation of the relations between sizes.  The four Qwen2-MoE keys the
 reference never reads (``decoder_sparse_step``, ``mlp_only_layers``,
 ``use_sliding_window``, ``max_window_layers``) are read here because they decide
-the per-layer choice of feed-forward and attention span.
+the per-layer choice of feed-forward and attention span.  Which layers slide is
+taken from ``layer_types`` when the file lists it, the way the reference reads that
+key (src/model/config.cc:438-456, include/inferx/model/config.h:196-203).
 """
 from __future__ import annotations
 
 import json
 import os
-from dataclasses import dataclass, asdict
+from dataclasses import dataclass, asdict, replace
 from typing import Any, Mapping
+
+
+FULL, SLIDING = "full_attention", "sliding_attention"
 
 
 class ConfigError(ValueError):
@@ -64,6 +69,12 @@ class _Reader:
             raise ConfigError(f"{self.where}: '{key}' must be a string, got {v!r}")
         return v
 
+    def string_list(self, key: str, default: Any = _MISSING) -> tuple:
+        v = self._get(key, default)
+        if not isinstance(v, (list, tuple)) or any(not isinstance(x, str) for x in v):
+            raise ConfigError(f"{self.where}: '{key}' must be a list of strings, got {v!r}")
+        return tuple(v)
+
     def int_list(self, key: str, default: Any = _MISSING) -> tuple:
         v = self._get(key, default)
         if not isinstance(v, (list, tuple)) or any(
@@ -110,6 +121,9 @@ class Qwen2MoeConfig:
     torch_dtype: str
     eos_token_ids: tuple = ()
     architecture: str = "Qwen2MoeForCausalLM"
+    # per layer "full_attention" | "sliding_attention": as listed in config.json, else
+    # derived once by ``from_json`` (see ``layer_window``)
+    layer_types: tuple = ()
 
     ARCHITECTURE = "Qwen2MoeForCausalLM"
 
@@ -124,10 +138,24 @@ class Qwen2MoeConfig:
         )
 
     def layer_window(self, i: int) -> int:
-        """Keys a query may see in layer ``i`` including itself; 0 means all."""
-        if self.use_sliding_window and self.sliding_window > 0 and i >= self.max_window_layers:
-            return self.sliding_window
-        return 0
+        """Keys a query may see in layer ``i`` including itself; 0 means all.
+
+        No layer slides unless ``use_sliding_window`` is set and ``sliding_window`` is
+        positive (the reference: no window, no sliding layer, config.h:196-203).  Then
+        ``layer_types[i]`` decides where config.json lists it (config.cc:438-456).
+        Without the list the layers from ``max_window_layers`` on slide and the ones
+        before it attend to everything: the rule of this engine, since the reference
+        has none for this architecture.  Folders written by this package always carry
+        the list, so that no reader has to derive it."""
+        if not (self.use_sliding_window and self.sliding_window > 0):
+            return 0
+        return self.sliding_window if self.layer_types[i] == SLIDING else 0
+
+    def settled_keys(self) -> dict:
+        """Keys whose value this engine had to derive by a rule of its own; whoever
+        writes a model folder from this configuration states them, so that every
+        reader of the folder runs the same layers the same way."""
+        return {"layer_types": list(self.layer_types)}
 
     # ---- parsing ------------------------------------------------------------
     @classmethod
@@ -208,7 +236,13 @@ class Qwen2MoeConfig:
             max_position_embeddings=r.integer("max_position_embeddings", 0),
             torch_dtype=dtype,
             eos_token_ids=_eos_ids(obj, where),
+            layer_types=r.string_list("layer_types", ()),
         )
+        if not cfg.layer_types:
+            slides = cfg.use_sliding_window and cfg.sliding_window > 0
+            cfg = replace(cfg, layer_types=tuple(
+                SLIDING if slides and i >= cfg.max_window_layers else FULL
+                for i in range(max(0, layers))))
         cfg.validate(where)
         return cfg
 
@@ -249,6 +283,14 @@ class Qwen2MoeConfig:
             need(self.sliding_window > 0, "'use_sliding_window' needs 'sliding_window' > 0")
             need(0 <= self.max_window_layers <= self.num_hidden_layers,
                  "'max_window_layers' must lie in [0, num_hidden_layers]")
+        need(len(self.layer_types) == self.num_hidden_layers,
+             f"'layer_types' has {len(self.layer_types)} entries for "
+             f"{self.num_hidden_layers} layers")
+        for t in self.layer_types:
+            # an unknown kind of layer is refused, never run as another
+            # (src/model/config.cc:452-454)
+            need(t in (FULL, SLIDING),
+                 f"unknown layer_type {t!r} (known: {FULL!r}, {SLIDING!r})")
         need(self.torch_dtype in ("bfloat16", "float32", "float16"),
              f"'torch_dtype' {self.torch_dtype!r} is not bfloat16/float16/float32")
 
@@ -256,6 +298,9 @@ class Qwen2MoeConfig:
         d = asdict(self)
         arch = d.pop("architecture")
         d["mlp_only_layers"] = list(self.mlp_only_layers)
+        # written out whether it was read or derived: the list settles which layers
+        # slide for every reader of the folder
+        d["layer_types"] = list(self.layer_types)
         eos = d.pop("eos_token_ids")
         if eos:
             d["eos_token_id"] = list(eos) if len(eos) > 1 else eos[0]

@@ -46,6 +46,11 @@ def write_random_model(config_json: Mapping, out_dir: str, seed: int, std: float
         raise ValueError(f"storage dtype {store_name!r} is not one of {sorted(_STORE)}")
     cfg["torch_dtype"] = store_name
     store = _STORE[store_name]
+    from ..config.registry import config_from_json
+    typed, _ = config_from_json(cfg)
+    # what the typed configuration derived by a rule of its own is stated in the folder
+    for key, value in getattr(typed, "settled_keys", dict)().items():
+        cfg.setdefault(key, value)
     decls = declared_tensors(cfg)
     src = RandomSource(seed, std=std, device="cpu")
     os.makedirs(out_dir, exist_ok=True)

@@ -35,6 +35,12 @@ TINY_B = {
 }
 
 
+# Tiny B with the sliding layers listed in config.json, and listed differently from what
+# the max_window_layers rule would derive: the window is on layers 0 and 2.
+TINY_B_LISTED = dict(TINY_B, layer_types=["sliding_attention", "full_attention",
+                                          "sliding_attention"])
+
+
 @pytest.fixture
 def tiny_a():
     return dict(TINY_A)

@@ -63,10 +63,20 @@ def layer_is_sparse(cfg, i):
 
 
 def layer_window(cfg, i):
-    """Window W (keys max(0,p-W+1)..p) on layers >= max_window_layers when
-    use_sliding_window; 0 = all keys."""
-    if cfg.get("use_sliding_window", False) and cfg.get("sliding_window", 0) > 0 \
-            and i >= cfg.get("max_window_layers", cfg["num_hidden_layers"]):
+    """Window W (keys max(0,p-W+1)..p) of layer i; 0 = all keys.  Nothing slides
+    without use_sliding_window and a positive sliding_window
+    (include/inferx/model/config.h:196-203: no window, no sliding layer).  With them,
+    the entry of "layer_types" decides when config.json has that list
+    (src/model/config.cc:438-456); a file without the list slides on the layers from
+    max_window_layers on."""
+    if not cfg.get("use_sliding_window", False) or cfg.get("sliding_window", 0) <= 0:
+        return 0
+    kinds = cfg.get("layer_types")
+    if kinds:
+        if kinds[i] not in ("full_attention", "sliding_attention"):
+            raise ValueError(f"unknown layer_type {kinds[i]!r}")
+        return cfg["sliding_window"] if kinds[i] == "sliding_attention" else 0
+    if i >= cfg.get("max_window_layers", cfg["num_hidden_layers"]):
         return cfg["sliding_window"]
     return 0
 

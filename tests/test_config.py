@@ -129,3 +129,37 @@ def test_from_dir_and_duplicate_keys(tmp_path, tiny_b):
         config_from_dir(str(tmp_path))
     with pytest.raises(ConfigError, match="no config.json"):
         config_from_dir(str(tmp_path / "missing"))
+
+
+def test_layer_types_decides_which_layers_slide(tiny_b):
+    """config.json's own list wins over the max_window_layers rule
+    (src/model/config.cc:438-456); without it the rule is stated in what is written."""
+    derived, _ = config_from_json(tiny_b)
+    assert [derived.layer_window(i) for i in range(3)] == [0, 8, 8]
+    assert derived.to_json()["layer_types"] == [
+        "full_attention", "sliding_attention", "sliding_attention"]
+    listed, spec = config_from_json(dict(tiny_b, layer_types=[
+        "sliding_attention", "full_attention", "full_attention"]))
+    assert [listed.layer_window(i) for i in range(3)] == [8, 0, 0]
+    assert [ls.mixer.window for ls in spec.layers] == [8, 0, 0]
+    # a list without a window slides nowhere (include/inferx/model/config.h:196-203)
+    off, _ = config_from_json(dict(tiny_b, use_sliding_window=False, layer_types=[
+        "sliding_attention"] * 3))
+    assert [off.layer_window(i) for i in range(3)] == [0, 0, 0]
+    with pytest.raises(ConfigError, match="2 entries for 3 layers"):
+        config_from_json(dict(tiny_b, layer_types=["full_attention"] * 2))
+    with pytest.raises(ConfigError, match="unknown layer_type 'chunked_attention'"):
+        config_from_json(dict(tiny_b, layer_types=["full_attention", "chunked_attention",
+                                                   "full_attention"]))
+    with pytest.raises(ConfigError, match="list of strings"):
+        config_from_json(dict(tiny_b, layer_types=[0, 1, 1]))
+
+
+def test_random_model_folder_states_layer_types(tmp_path, tiny_b):
+    from inferx_b200.weights.random_model import write_random_model
+    write_random_model(tiny_b, str(tmp_path / "m"), seed=0)
+    written = json.loads((tmp_path / "m" / "config.json").read_text())
+    assert written["layer_types"] == ["full_attention", "sliding_attention", "sliding_attention"]
+    mine = ["sliding_attention", "full_attention", "sliding_attention"]
+    write_random_model(dict(tiny_b, layer_types=mine), str(tmp_path / "n"), seed=0)
+    assert json.loads((tmp_path / "n" / "config.json").read_text())["layer_types"] == mine

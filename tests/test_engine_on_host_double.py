@@ -9,10 +9,11 @@ import torch
 import host_ops
 import model_cases as mc
 import traces
-from conftest import TINY_A, TINY_B
+from conftest import TINY_A, TINY_B, TINY_B_LISTED
 from inferx_b200.engine.replay import ReplaySession
 
-CASES = [("A", TINY_A, 0, [5, 9, 17, 40, 3, 70], 4), ("B", TINY_B, 1, [1, 6, 13, 31, 45, 80], 8)]
+CASES = [("A", TINY_A, 0, [5, 9, 17, 40, 3, 70], 4), ("B", TINY_B, 1, [1, 6, 13, 31, 45, 80], 8),
+         ("B-listed", TINY_B_LISTED, 2, [2, 29, 11, 52], 8)]
 
 
 @pytest.mark.parametrize("name,cfg,seed,lengths,page", CASES)

@@ -12,12 +12,13 @@ import torch
 
 import model_cases as mc
 import traces
-from conftest import ROOT, TINY_A, TINY_B
+from conftest import ROOT, TINY_A, TINY_B, TINY_B_LISTED
 from inferx_b200.engine.replay import ReplaySession
 
 pytestmark = pytest.mark.gpu
 
-CASES = [("A", TINY_A, 0, [5, 9, 17, 40, 3, 70], 4), ("B", TINY_B, 1, [1, 6, 13, 31, 45, 80], 8)]
+CASES = [("A", TINY_A, 0, [5, 9, 17, 40, 3, 70], 4), ("B", TINY_B, 1, [1, 6, 13, 31, 45, 80], 8),
+         ("B-listed", TINY_B_LISTED, 2, [2, 29, 11, 52], 8)]
 # Error bounds relative to the largest logit of the request: fp32 differs from the plain
 # implementation only by summation order (2e-5); the bfloat16 bound is derived per model
 # from what bfloat16 storage costs the plain model itself (model_cases.bf16_bound).
