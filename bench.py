@@ -180,8 +180,9 @@ def fill_context(rt, batch, context):
     mgr = rt.manager
     for rid in list(mgr.live_requests()):
         mgr.close(rid)
-    for t in list(rt.storage.k.values()) + list(rt.storage.v.values()):
-        t.normal_(0.0, 0.5)
+    for per in rt.storage.paged.values():
+        for t in per.values():
+            t.normal_(0.0, 0.5)
     for i in range(batch):
         mgr.open(i)
         assert mgr.reserve(i, context - 1)

@@ -148,6 +148,10 @@ class CacheManager:
     def slot(self, rid) -> int:
         return self._req(rid).slot
 
+    def first_live(self, rid, group: int) -> int:
+        """Index of the first page of the request this group still holds."""
+        return self._req(rid).first_live[group]
+
     def table(self, rid, group: int) -> "array":
         """The request's block table in this group: an ``array('i')`` of page ids (it
         reads like a list and hands its memory to numpy without a copy)."""
@@ -235,14 +239,21 @@ class CacheManager:
             raise CacheError("a state slot was lost")
 
 
+def is_paged_need(need) -> bool:
+    """A need kept per token in pages (it says how long tokens are kept and how wide a
+    token's record is), as opposed to state of fixed size per request."""
+    return hasattr(need, "window") and hasattr(need, "kv_heads") and hasattr(need, "head_dim")
+
+
 def groups_for(cache_needs_per_layer) -> List[CacheGroup]:
     """Group layers by the span of tokens their paged needs keep.
 
-    ``cache_needs_per_layer[i]`` is the list of needs of layer ``i``'s mixer;
-    objects with a ``window`` attribute are paged needs."""
+    ``cache_needs_per_layer[i]`` is the list of needs of layer ``i``'s mixer.  The span
+    alone decides the group: a page is a span of tokens, so layers whose records differ
+    in shape or number of entries can share page numbers and block tables."""
     by_window: Dict[int, List[int]] = {}
     for i, needs in enumerate(cache_needs_per_layer):
         for need in needs:
-            if hasattr(need, "window") and hasattr(need, "kv_heads"):
-                by_window.setdefault(int(need.window), []).append(i)
+            if is_paged_need(need) and i not in by_window.setdefault(int(need.window), []):
+                by_window[int(need.window)].append(i)
     return [CacheGroup(window=w, layers=tuple(ls)) for w, ls in sorted(by_window.items())]

@@ -1,11 +1,11 @@
 """Device memory behind the cache manager's bookkeeping.
 
-Per layer that writes keys and values: two tensors ``[pages, kv_heads,
-page_size, head_dim]`` indexed by the page ids of the layer's group (the
-reference's per-layer views are ``[P, B, kv_heads, hd]``,
-include/inferx/core/kv_cache.h:40-150; heads are moved outward here so that one
-head's part of a page is contiguous).  Per state need of a mixer: one tensor
-``[slots, *shape]``.  Everything starts from zero; a slot is zeroed again when it
+Per layer with a paged need: one tensor ``[pages, kv_heads, page_size, head_dim]``
+for each entry of the need (keys and values for attention; whatever a mixer names),
+indexed by the page ids of the layer's group (the reference's per-layer views are
+``[P, B, kv_heads, hd]``, include/inferx/core/kv_cache.h:40-150; heads are moved
+outward here so that one head's part of a page is contiguous).  Per state need of a
+mixer: one tensor ``[slots, *shape]``.  Everything starts from zero; a slot is zeroed again when it
 is handed to a new request.
 """
 from __future__ import annotations
@@ -15,28 +15,32 @@ from typing import Dict, List
 import torch
 
 from ..parts.base import LayerCache, PagedKvNeed, StateNeed
-from .manager import CacheManager
+from .manager import CacheManager, is_paged_need
 
 
 class CacheStorage:
     def __init__(self, cache_needs_per_layer, manager: CacheManager, dtype: torch.dtype, device):
         self.manager = manager
         self.device = torch.device(device)
-        self.k: Dict[int, torch.Tensor] = {}
-        self.v: Dict[int, torch.Tensor] = {}
+        self.paged: Dict[int, Dict[str, torch.Tensor]] = {}
         self.group_of_layer: Dict[int, int] = {}
         self.state: Dict[int, Dict[str, torch.Tensor]] = {}
         window_to_group = {g.window: i for i, g in enumerate(manager.groups)}
         for layer, needs in enumerate(cache_needs_per_layer):
             for need in needs:
-                if isinstance(need, PagedKvNeed) or (hasattr(need, "kv_heads")
-                                                     and hasattr(need, "window")):
+                if is_paged_need(need):
                     g = window_to_group[int(need.window)]
+                    if self.group_of_layer.setdefault(layer, g) != g:
+                        raise TypeError(f"layer {layer}: paged needs with different windows; "
+                                        "one block table addresses a layer's pages")
                     pages = manager.pools[g].num_pages
                     shape = (pages, need.kv_heads, manager.page_size, need.head_dim)
-                    self.k[layer] = torch.zeros(shape, dtype=dtype, device=self.device)
-                    self.v[layer] = torch.zeros(shape, dtype=dtype, device=self.device)
-                    self.group_of_layer[layer] = g
+                    per = self.paged.setdefault(layer, {})
+                    for name in getattr(need, "entries", ("k", "v")):
+                        if name in per:
+                            raise TypeError(f"layer {layer}: paged entry {name!r} named twice")
+                        per[name] = torch.zeros(shape, dtype=getattr(need, "dtype", None) or dtype,
+                                                device=self.device)
                 elif isinstance(need, StateNeed) or hasattr(need, "shape"):
                     self.state.setdefault(layer, {})[need.name] = torch.zeros(
                         (manager.max_slots,) + tuple(need.shape), dtype=need.dtype,
@@ -46,8 +50,8 @@ class CacheStorage:
 
     def bytes(self) -> int:
         n = 0
-        for d in (self.k, self.v):
-            n += sum(t.numel() * t.element_size() for t in d.values())
+        for per in self.paged.values():
+            n += sum(t.numel() * t.element_size() for t in per.values())
         for per in self.state.values():
             n += sum(t.numel() * t.element_size() for t in per.values())
         return n
@@ -58,7 +62,7 @@ class CacheStorage:
         for e in schedule:
             src = e.cache_layer
             out.append(LayerCache(
-                group=self.group_of_layer.get(src, -1), k=self.k.get(src), v=self.v.get(src),
+                group=self.group_of_layer.get(src, -1), pages=self.paged.get(src, {}),
                 writes=e.writes_cache, state=self.state.get(src, {})))
         return out
 

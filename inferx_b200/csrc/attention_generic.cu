@@ -99,6 +99,10 @@ paged_attention_generic_kernel(const TA* __restrict__ q, const TA* __restrict__ 
   }
 }
 
+// The largest head size any attention kernel of this library takes (this one; the tuned
+// kernels take fewer); a model is checked against it when it is built.
+IX_API int ix_attention_max_head_dim() { return ATT_THREADS * ATT_MAX_DPT; }
+
 IX_API int ix_paged_attention_generic(const void* q, const void* k_cache, const void* v_cache,
                                       const int* block_table, const int* seq_of_token,
                                       const int* positions, void* out, int act_dtype, int T,

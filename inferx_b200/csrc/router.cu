@@ -19,6 +19,7 @@
 #define ROUTER_THREADS 256
 #define ROUTER_MAX_TOK 8
 #define ROUTER_MAX_TOPK 32
+#define ROUTER_MAX_EXPERTS 8192   // the dispatch kernels' histogram
 
 // Softmax over p[0..E) (logits, overwritten), then k rounds of masked argmax by one
 // warp; ties go to the lower index.  Writes k weights and k expert ids.
@@ -285,6 +286,11 @@ router_select_kernel(const float* __restrict__ logits, int E, int k, int renorm,
   select_topk(prob, E, k, renorm, scale, topk_w + (size_t)t * k, topk_idx + (size_t)t * k, lane);
 }
 
+// Sizes beyond which the router and dispatch kernels refuse a call; a model is checked
+// against them when it is built.
+IX_API int ix_router_max_topk() { return ROUTER_MAX_TOPK; }
+IX_API int ix_router_max_experts() { return ROUTER_MAX_EXPERTS; }
+
 IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, int act_dtype,
                           int T, int H, int E, int k, int renorm, float scale, float* topk_w,
                           int* topk_idx, float* extra_out, float* logits_scratch,
@@ -484,7 +490,7 @@ IX_API int ix_moe_dispatch_scratch_ints(int T, int E, int k) {
 
 IX_API int ix_moe_dispatch(const int* topk_idx, int T, int E, int k, int* offsets, int* rows,
                            int* dest, int* scratch, cudaStream_t stream) {
-  if (E <= 0 || k <= 0 || E > 8192) return IX_ERR_SIZE;
+  if (E <= 0 || k <= 0 || E > ROUTER_MAX_EXPERTS) return IX_ERR_SIZE;
   if (T < 0) return IX_ERR_SIZE;
   const int A = T * k;
   if (scratch && A > 512 && E <= DISPATCH_MAX_E) {

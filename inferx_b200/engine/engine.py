@@ -17,7 +17,7 @@ from typing import Any, Dict, Hashable, Iterator, List, Mapping, Optional, Seque
 
 import torch
 
-from ..cache.manager import groups_for
+from ..cache.manager import is_paged_need, groups_for
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from ..weights.loader import RandomSource
@@ -56,19 +56,32 @@ class Request:
 
 
 def cache_bytes_per_page(model, page_size: int) -> List[int]:
-    """Bytes one page costs in each cache group (all layers of the group, K and V)."""
+    """Bytes one page costs in each cache group (every entry of every layer of the
+    group)."""
     needs = model.cache_needs()
     groups = groups_for(needs)
-    esize = 2 if model.ctx.dtype == torch.bfloat16 else 4
     out = []
     for g in groups:
         b = 0
         for layer in g.layers:
             for need in needs[layer]:
-                if hasattr(need, "kv_heads") and int(need.window) == g.window:
-                    b += 2 * need.kv_heads * need.head_dim * page_size * esize
+                if is_paged_need(need) and int(need.window) == g.window:
+                    b += need.bytes_per_token(model.ctx.dtype) * page_size
         out.append(b)
     return out
+
+
+def graph_reserve_bytes(cfg: EngineConfig, model) -> int:
+    """Device memory to leave for recorded steps: each kept graph holds the logits of its
+    wanted rows (at most one row per resident sequence, fp32 over the vocabulary), and
+    all of them share one pool of activations sized by the largest step (some dozens of
+    bytes per token and unit of width, taken generously)."""
+    from .executor import GraphCache
+    limits = GraphCache().limits
+    spec = model.spec
+    logits = (limits[True] + limits[False]) * cfg.max_num_seqs * spec.vocab_size * 4
+    activations = cfg.batched_tokens() * spec.hidden * 64
+    return logits + activations
 
 
 def autosize_pages(cfg: EngineConfig, model, device) -> int:
@@ -84,6 +97,8 @@ def autosize_pages(cfg: EngineConfig, model, device) -> int:
     free, total = torch.cuda.mem_get_info(device)
     used = total - free
     budget = int(cfg.gpu_memory_utilization * total) - used - (1 << 30)
+    if not cfg.enforce_eager:
+        budget -= graph_reserve_bytes(cfg, model)
     # no more than every resident sequence at full length can use
     want = cfg.max_num_seqs * floor
     return max(floor, min(want, budget // per_page))

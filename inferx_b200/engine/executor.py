@@ -80,6 +80,8 @@ class _Layout:
     kv_lens: List[int]
     wanted: Tuple[int, ...]
     num_decode: int = 0        # sequences with a single token; they come first
+    state_slots: Tuple[int, ...] = ()
+    first_live: Tuple[Tuple[int, ...], ...] = ()   # per group, per sequence
 
 
 @dataclass
@@ -90,6 +92,60 @@ class _Graph:
     copied: List[Optional["torch.cuda.Event"]]
     logits: Optional[torch.Tensor]
     turn: int = 0
+
+
+class GraphCache:
+    """Which step shapes are kept as recorded CUDA graphs, and for how long.
+
+    A step's shape is: how many tokens each sequence brings (in batch order), the width
+    of each group's block table (rounded up to a bucket) and the wanted rows.  Steps of
+    single tokens are recorded the second time their shape is seen; other shapes (prompt
+    portions, mixed batches) the third time: prompts rarely repeat a shape exactly,
+    except for full portions of long prompts and for benchmarks.  Both kinds are kept
+    least-recently-used up to a bound of their own, because every recorded step holds
+    device memory (its index arrays, its logits, its share of the graph pool): a serving
+    run whose batch sizes and contexts wander would otherwise keep one for every
+    (batch size, table width) it ever met.  (The reference records a fixed list of decode
+    shapes at start-up, src/model/qwen2.cc:1588-1712.)  Pure bookkeeping: it never
+    touches a device."""
+
+    def __init__(self, decode_graphs: int = 64, prompt_graphs: int = 4,
+                 decode_seen: int = 2, prompt_seen: int = 3, seen_shapes: int = 4096):
+        self.limits = {True: int(decode_graphs), False: int(prompt_graphs)}
+        self.need_seen = {True: int(decode_seen), False: int(prompt_seen)}
+        self.seen_shapes = int(seen_shapes)
+        self._kept = {True: {}, False: {}}     # decode? -> {key: graph}; oldest first
+        self._seen: Dict[Tuple, int] = {}
+        self.evictions = 0
+
+    def __len__(self) -> int:
+        return len(self._kept[True]) + len(self._kept[False])
+
+    def count(self, decode: bool) -> int:
+        return len(self._kept[decode])
+
+    def get(self, key):
+        """The recorded step of this shape, marked most recently used; or None."""
+        for kept in self._kept.values():
+            if key in kept:
+                kept[key] = kept.pop(key)      # dicts keep insertion order: last = newest
+                return kept[key]
+        return None
+
+    def should_record(self, key, decode: bool) -> bool:
+        """Count a sighting of a shape that is not kept; True when it is due."""
+        if len(self._seen) >= self.seen_shapes:
+            self._seen.clear()
+        n = self._seen[key] = self._seen.get(key, 0) + 1
+        return n >= self.need_seen[decode]
+
+    def put(self, key, graph, decode: bool) -> None:
+        kept = self._kept[decode]
+        while len(kept) >= max(1, self.limits[decode]):
+            del kept[next(iter(kept))]         # the least recently used goes
+            self.evictions += 1
+        kept[key] = graph
+        self._seen.pop(key, None)
 
 
 class Executor:
@@ -103,8 +159,8 @@ class Executor:
         self.caches = storage.layer_caches(model.spec.schedule)
         self.steps_run = 0
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
-        self._graphs: Dict[Tuple, _Graph] = {}
-        self._seen: Dict[Tuple, int] = {}
+        self._graphs = GraphCache()
+        self._graph_pool = None
         self.graph_replays = 0
         self.last_h2d_bytes = 0
 
@@ -228,7 +284,10 @@ class Executor:
                     view[s, :len(row)] = np.frombuffer(row, dtype=np.int32)
         return _Layout(T=T, S=S, R=R, buf=buf, offs=offs, lens=lens, total=total, widths=widths,
                        q_lens=q_lens, kv_lens=[a + n for a, n in zip(starts, q_lens)],
-                       wanted=tuple(wanted), num_decode=num_decode)
+                       wanted=tuple(wanted), num_decode=num_decode,
+                       state_slots=tuple(int(x) for x in state_slot),
+                       first_live=tuple(tuple(mgr.first_live(entries[i].request, g)
+                                              for i in order) for g in range(n_groups)))
 
     @staticmethod
     def _fill(host: torch.Tensor, lay: _Layout) -> None:
@@ -244,7 +303,8 @@ class Executor:
         for g, grp in enumerate(mgr.groups):
             groups.append(GroupView(
                 block_table=seg(_FIXED_SEGS + 2 * g + 1).view(lay.S, lay.widths[g]),
-                slots=seg(_FIXED_SEGS + 2 * g), page_size=mgr.page_size, window=grp.window))
+                slots=seg(_FIXED_SEGS + 2 * g), page_size=mgr.page_size, window=grp.window,
+                first_live=None if static else list(lay.first_live[g])))
         max_kv = max(lay.kv_lens)
         if static:   # a captured graph must hold for every length its table width allows
             max_kv = max(w for w in lay.widths) * mgr.page_size if lay.widths else max_kv
@@ -253,7 +313,8 @@ class Executor:
             seq_of_token=seg(_SEQ_OF_TOKEN), cu_q=seg(_CU_Q), q_pos0=seg(_Q_POS0),
             kv_len=seg(_KV_LEN), state_slot=seg(_STATE_SLOT),
             groups=groups, max_q_len=max(lay.q_lens), max_kv_len=max_kv,
-            q_lens=list(lay.q_lens), kv_lens=list(lay.kv_lens),
+            q_lens=list(lay.q_lens), kv_lens=None if static else list(lay.kv_lens),
+            state_slots=None if static else list(lay.state_slots), captured=static,
             all_decode=all(n == 1 for n in lay.q_lens), num_decode_seqs=lay.num_decode,
             cu_q_prompt=seg(_CU_Q_PROMPT))
         return ctx, (seg(_LOGIT_ROWS) if lay.R else None)
@@ -271,43 +332,22 @@ class Executor:
         return ctx, rows, lay.R
 
     # ------------------------------------------------------------------
-    # A step's shape: how many tokens each sequence brings (in batch order), the width of
-    # each group's block table (rounded up to a bucket) and the wanted rows.  Steps of
-    # single tokens are captured into a CUDA graph the second time their shape is seen;
-    # other shapes (prompt portions, mixed batches) the third time, and at most
-    # PROMPT_GRAPHS of them are kept (the least recently used goes): prompts rarely
-    # repeat a shape exactly, except for full portions of long prompts and for
-    # benchmarks.
-    PROMPT_GRAPHS = 4
-    SEEN_SHAPES = 4096
-    DECODE_SEEN = 2       # a shape is captured when it is seen this many times
-    PROMPT_SEEN = 3
-
     def _graph_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         lay = self._layout(entries, bucket_tables=True)
-        wanted = lay.wanted
         decode = lay.num_decode == lay.S
-        key = (lay.S if decode else tuple(lay.q_lens), tuple(lay.widths), wanted)
+        key = (lay.S if decode else tuple(lay.q_lens), tuple(lay.widths), lay.wanted)
         slot = self._graphs.get(key)
-        if slot is None:
-            if len(self._seen) >= self.SEEN_SHAPES:
-                self._seen.clear()
-            seen = self._seen[key] = self._seen.get(key, 0) + 1
-            if seen < (self.DECODE_SEEN if decode else self.PROMPT_SEEN):
-                # The first step of a shape runs eagerly: kernels are loaded, attributes
-                # set and the library's plans made outside of any capture.
-                host = torch.zeros(lay.total, dtype=torch.int32).pin_memory()
-                self._fill(host, lay)
-                dev = host.to(self.device, non_blocking=True)
-                self.last_h2d_bytes = lay.total * 4
-                ctx, rows = self._context(dev, lay, static=True)
-                return self.model.forward(ctx, self.caches, rows)
-            if not decode:
-                prompts = [k for k in self._graphs if not isinstance(k[0], int)]
-                if len(prompts) >= self.PROMPT_GRAPHS:
-                    del self._graphs[prompts[0]]      # dicts keep insertion order: the oldest
-        elif not decode:
-            self._graphs[key] = self._graphs.pop(key)  # most recently used goes last
+        if slot is None and not self._graphs.should_record(key, decode):
+            # The first step of a shape runs eagerly: kernels are loaded, attributes
+            # set and the library's plans made outside of any capture.  It is built like
+            # a recorded step (bucketed tables, no per-step host values), so that a part
+            # which cannot be recorded fails here, at the first step, and not later.
+            host = torch.zeros(lay.total, dtype=torch.int32).pin_memory()
+            self._fill(host, lay)
+            dev = host.to(self.device, non_blocking=True)
+            self.last_h2d_bytes = lay.total * 4
+            ctx, rows = self._context(dev, lay, static=True)
+            return self.model.forward(ctx, self.caches, rows)
         if slot is None:
             host = torch.zeros(lay.total, dtype=torch.int32).pin_memory()
             dev = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
@@ -315,12 +355,17 @@ class Executor:
             dev.copy_(host, non_blocking=True)
             ctx, rows = self._context(dev, lay, static=True)
             torch.cuda.current_stream(self.device).synchronize()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            # One memory pool for all recorded steps: they run one after the other, so
+            # their activations can live in the same memory; a step's logits stay
+            # allocated while its graph is kept and are not handed to a later recording.
+            with torch.cuda.graph(graph, pool=self._graph_pool):
                 logits = self.model.forward(ctx, self.caches, rows)
             slot = _Graph(graph, dev, [host, torch.zeros_like(host).pin_memory()], [None, None],
                           logits)
-            self._graphs[key] = slot
+            self._graphs.put(key, slot, decode)
         else:
             i = slot.turn = 1 - slot.turn
             if slot.copied[i] is not None:

@@ -119,6 +119,34 @@ def set_dependent_launch(on: bool) -> None:
 
 
 # ---------------------------------------------------------------------------
+# Sizes the kernels refuse.  Parts call these when a model is built, so that a model the
+# kernels cannot run is refused with the offending size named, before weights are read;
+# the kernels' own checks remain (they return "a size this kernel does not take").
+def check_attention_limits(heads: int, kv_heads: int, head_dim: int, dtype, where: str = ""):
+    lib = _lib()
+    most = lib.ix_attention_max_head_dim()
+    if head_dim > most:
+        raise KernelError(f"{where}: head size {head_dim} exceeds the largest the attention "
+                          f"kernels take ({most})")
+    if head_dim % 2:
+        raise KernelError(f"{where}: head size {head_dim} is odd")
+    if heads > 65535 or heads % max(1, kv_heads):
+        raise KernelError(f"{where}: {heads} heads over {kv_heads} key/value heads is not a "
+                          "grouping the attention kernels take (a multiple, at most 65535)")
+
+
+def check_router_limits(hidden: int, num_experts: int, top_k: int, where: str = ""):
+    lib = _lib()
+    if top_k > lib.ix_router_max_topk():
+        raise KernelError(f"{where}: {top_k} experts per token exceed the router kernel's "
+                          f"limit of {lib.ix_router_max_topk()}")
+    if num_experts > lib.ix_router_max_experts():
+        raise KernelError(f"{where}: {num_experts} experts exceed the dispatch kernels' limit "
+                          f"of {lib.ix_router_max_experts()}")
+    if top_k > num_experts:
+        raise KernelError(f"{where}: {top_k} experts per token of {num_experts}")
+
+
 def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None):
     """out[t] = table[ids[t]] widened to fp32 (the residual stream)."""
     _chk("table", table)

@@ -33,7 +33,10 @@ def build_spec(cfg: Qwen2MoeConfig) -> ModelSpec:
                 hidden=cfg.hidden_size, num_experts=cfg.num_experts,
                 top_k=cfg.num_experts_per_tok, expert_intermediate=cfg.moe_intermediate_size,
                 renormalize=cfg.norm_topk_prob, routed_scale=1.0,
-                shared_intermediate=cfg.shared_expert_intermediate_size, shared_gated=True)
+                shared=(SwiGluSpec(hidden=cfg.hidden_size,
+                                   intermediate=cfg.shared_expert_intermediate_size)
+                        if cfg.shared_expert_intermediate_size > 0 else None),
+                shared_gated=True)
         else:
             ffn = SwiGluSpec(hidden=cfg.hidden_size, intermediate=cfg.intermediate_size)
         layers.append(LayerSpec(prefix=f"model.layers.{i}", input_norm=norm, mixer=mixer,

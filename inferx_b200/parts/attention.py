@@ -24,6 +24,12 @@ class AttentionMixer:
         self.position = build_part("position", spec.position, ctx, prefix)
         self.qkv_w = self.qkv_b = self.o_w = None
 
+    def check_limits(self):
+        check = getattr(self.ctx.ops, "check_attention_limits", None)
+        if check is not None:
+            s = self.spec
+            check(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, self.prefix)
+
     # -- weights -----------------------------------------------------------
     def tensors(self):
         s, p = self.spec, self.prefix

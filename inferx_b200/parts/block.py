@@ -19,12 +19,14 @@ import torch
 from ..weights import loader as wl
 from ..weights.loader import TensorDecl
 from .base import BuildContext, LayerCache, StepContext
-from .registry import build_part
+from .registry import build_part, register_part
 
 
-class Block:
-    def __init__(self, spec, ctx: BuildContext):
-        p = spec.prefix
+class PreNormBlock:
+    """``x += mixer(norm(x)); x += ffn(norm(x))`` on the fp32 residual stream."""
+
+    def __init__(self, spec, ctx: BuildContext, prefix: str):
+        p = prefix
         self.spec = spec
         self.input_norm = build_part("norm", spec.input_norm, ctx, f"{p}.{spec.input_norm_name}")
         self.mixer = build_part("mixer", spec.mixer, ctx, f"{p}.{spec.mixer_name}")
@@ -33,6 +35,9 @@ class Block:
 
     def parts(self):
         return [self.input_norm, self.mixer, self.post_norm, self.ffn]
+
+    def cache_needs(self):
+        return list(self.mixer.cache_needs())
 
     def forward(self, resid, pending, step: StepContext, cache: LayerCache):
         """``pending`` is the previous block's contribution not yet added to
@@ -52,13 +57,19 @@ class DecoderModel:
     def __init__(self, spec, ctx: BuildContext):
         self.spec = spec
         self.ctx = ctx
-        self.blocks: List[Block] = [Block(ls, ctx) for ls in spec.layers]
+        self.blocks = [build_part("block", ls, ctx, ls.prefix) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, ctx, spec.final_norm_name)
         self.embed = None
         self.head = None
         for e in spec.schedule:
             if not (0 <= e.layer < len(self.blocks)) or not (0 <= e.cache_layer < len(self.blocks)):
                 raise ValueError(f"schedule entry {e} names a layer that does not exist")
+        if ctx.ops is not None:
+            # sizes beyond what the kernels take are refused now, not at the first launch
+            for b in self.blocks:
+                for part in b.parts():
+                    if hasattr(part, "check_limits"):
+                        part.check_limits()
 
     # -- weights -----------------------------------------------------------
     def _own_tensors(self) -> List[TensorDecl]:
@@ -95,7 +106,7 @@ class DecoderModel:
     # -- cache needs -------------------------------------------------------
     def cache_needs(self) -> List[list]:
         """Per layer, what its mixer wants kept between steps."""
-        return [list(b.mixer.cache_needs()) for b in self.blocks]
+        return [list(b.cache_needs()) for b in self.blocks]
 
     # -- step --------------------------------------------------------------
     def forward(self, step: StepContext, caches: List[LayerCache],
@@ -116,3 +127,7 @@ class DecoderModel:
             pending = pending.materialize()
         n = self.final_norm.forward(resid, pending, rows=logit_rows)
         return ops.linear(n, self.head, out_dtype=torch.float32)
+
+
+Block = PreNormBlock
+register_part("block", "pre_norm", PreNormBlock)

@@ -17,7 +17,7 @@ from __future__ import annotations
 import torch
 
 from ..weights.loader import TensorDecl
-from .registry import register_part
+from .registry import build_part, register_part
 
 
 class SwiGluFeedForward:
@@ -53,11 +53,17 @@ class MoeFeedForward:
         self.shared = None
         self.shared_gate_w = None
         self._side = None
-        if spec.shared_intermediate > 0:
-            from .specs import SwiGluSpec
-            self.shared = SwiGluFeedForward(
-                SwiGluSpec(hidden=spec.hidden, intermediate=spec.shared_intermediate), ctx,
-                f"{prefix}.shared_expert")
+        if spec.shared is not None:
+            # any registered feed-forward may serve as the shared expert
+            self.shared = build_part("feed_forward", spec.shared, ctx,
+                                     f"{prefix}.{spec.shared_name}")
+
+    def check_limits(self):
+        check = getattr(self.ctx.ops, "check_router_limits", None)
+        if check is not None:
+            check(self.spec.hidden, self.spec.num_experts, self.spec.top_k, self.prefix)
+        if self.shared is not None and hasattr(self.shared, "check_limits"):
+            self.shared.check_limits()
 
     def tensors(self):
         s, p = self.spec, self.prefix
@@ -71,7 +77,7 @@ class MoeFeedForward:
         if self.shared is not None:
             decls += self.shared.tensors()
             if s.shared_gated:
-                decls.append(TensorDecl(f"{p}.shared_expert_gate.weight", (1, s.hidden),
+                decls.append(TensorDecl(f"{p}.{s.shared_gate_name}.weight", (1, s.hidden),
                                         keep="float32"))
         return decls
 
@@ -88,9 +94,9 @@ class MoeFeedForward:
             dn[e] = w[f"{p}.experts.{e}.down_proj.weight"]
         self.expert_gate_up, self.expert_down = gu, dn
         if self.shared is not None:
-            self.shared.bind(w)
+            self.shared.bind({d.name: w[d.name] for d in self.shared.tensors()})
             if s.shared_gated:
-                self.shared_gate_w = w[f"{p}.shared_expert_gate.weight"].reshape(-1).contiguous()
+                self.shared_gate_w = w[f"{p}.{s.shared_gate_name}.weight"].reshape(-1).contiguous()
 
     # Below this many tokens a step's kernels leave the GPU partly idle; the shared
     # expert (which needs nothing from the router) then runs beside the routed experts.
@@ -109,7 +115,7 @@ class MoeFeedForward:
             main = torch.cuda.current_stream(x.device)
             side.wait_stream(main)
             with torch.cuda.stream(side):
-                shared = self.shared.forward(x)
+                shared = self.shared.forward(x, step)
         topk_w, topk_idx, shared_logit = ops.router_topk(
             x, self.router_w, s.top_k, s.renormalize, s.routed_scale, extra_w=self.shared_gate_w)
         offsets, rows, dest = ops.moe_dispatch(topk_idx, s.num_experts)
@@ -120,7 +126,7 @@ class MoeFeedForward:
         if side is not None:
             main.wait_stream(side)
         elif self.shared is not None:
-            shared = self.shared.forward(x)
+            shared = self.shared.forward(x, step)
         combine = getattr(ops, "moe_combine_pending", ops.moe_combine)
         return combine(y, dest, topk_w, shared, shared_logit)
 

@@ -1,6 +1,7 @@
 """Registry from (role, kind) to the class that runs a spec of that kind.
 
-Roles: ``"norm"``, ``"position"``, ``"mixer"``, ``"feed_forward"``.  A new kind
+Roles: ``"norm"``, ``"position"``, ``"mixer"``, ``"feed_forward"`` and ``"block"``
+(the arrangement of one layer's parts).  A new kind
 of part is added by registering its class here; nothing else in the package
 names the kinds.
 """
@@ -8,7 +9,7 @@ from __future__ import annotations
 
 from typing import Any, Dict
 
-ROLES = ("norm", "position", "mixer", "feed_forward")
+ROLES = ("norm", "position", "mixer", "feed_forward", "block")
 _PARTS: Dict[str, Dict[str, type]] = {r: {} for r in ROLES}
 
 

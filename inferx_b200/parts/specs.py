@@ -62,14 +62,17 @@ class MoeSpec:
     expert_intermediate: int
     renormalize: bool
     routed_scale: float
-    shared_intermediate: int  # 0 = no shared expert
-    shared_gated: bool
+    shared: Any               # a feed-forward spec run over every token, or None
+    shared_gated: bool        # its output scaled by sigmoid(x . w_gate)
+    shared_name: str = "shared_expert"
+    shared_gate_name: str = "shared_expert_gate"
     kind: str = "moe"
 
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One pre-norm residual block: x += mixer(norm(x)); x += ffn(norm(x))."""
+    """One layer: its parts, and ``kind``, the arrangement they run in.  "pre_norm" is
+    x += mixer(norm(x)); x += ffn(norm(x))."""
     prefix: str  # tensor-name prefix, e.g. "model.layers.3"
     input_norm: Any
     mixer: Any
@@ -80,6 +83,7 @@ class LayerSpec:
     mixer_name: str = "self_attn"
     post_norm_name: str = "post_attention_layernorm"
     ffn_name: str = "mlp"
+    kind: str = "pre_norm"
 
 
 @dataclass(frozen=True)

@@ -77,12 +77,77 @@ def _name_seed(seed: int, name: str) -> int:
     return int.from_bytes(h[:8], "little") & 0x7FFFFFFFFFFFFFFF
 
 
+_MASK64 = (1 << 64) - 1
+
+
+def _i64(v: int) -> int:
+    """A 64-bit pattern as the signed integer torch's int64 holds."""
+    v &= _MASK64
+    return v - (1 << 64) if v >> 63 else v
+
+
+_NORMAL_CELLS = 1 << 16
+_normal_quantiles: dict = {}
+
+
+def _quantile_table(device) -> torch.Tensor:
+    """Quantiles of the standard normal at j / 65536, j = 0..65536, as float64; the two
+    ends, where the quantile is infinite, hold that of a quarter of a cell (4.8 standard
+    deviations).  Computed once on the host by Wichura's algorithm in plain Python
+    (``statistics.NormalDist``) and copied to the device, so every device draws from the
+    same numbers."""
+    key = str(device)
+    if key not in _normal_quantiles:
+        if "cpu" not in _normal_quantiles:
+            from statistics import NormalDist
+            inv = NormalDist().inv_cdf
+            n = _NORMAL_CELLS
+            end = inv(0.25 / n)
+            _normal_quantiles["cpu"] = torch.tensor(
+                [end] + [inv(j / n) for j in range(1, n)] + [-end], dtype=torch.float64)
+        _normal_quantiles[key] = _normal_quantiles["cpu"].to(device)
+    return _normal_quantiles[key]
+
+
+def _lsr(z: torch.Tensor, n: int) -> torch.Tensor:
+    """Logical shift right of int64 values (torch's ``>>`` carries the sign)."""
+    return (z >> n) & ((1 << (64 - n)) - 1)
+
+
+def counter_normal(key: int, numel: int, device, chunk: int = 1 << 24) -> torch.Tensor:
+    """``numel`` standard-normal fp64 values that depend on (key, index) only.
+
+    Element i hashes the counter ``key + (i + 1) * golden`` with the splitmix64
+    finaliser; the top 16 bits of the hash choose a cell of the inverse normal
+    distribution function, the next 32 bits a place inside the cell by linear
+    interpolation.  Integer arithmetic that wraps, a table look-up and three IEEE
+    double operations: the same bits on the CPU and on a CUDA device, in any order of
+    generation, which a library's generator does not give."""
+    table = _quantile_table(device)
+    out = torch.empty(numel, dtype=torch.float64, device=device)
+    golden, m1, m2 = _i64(0x9E3779B97F4A7C15), _i64(0xBF58476D1CE4E5B9), _i64(0x94D049BB133111EB)
+    for lo in range(0, numel, chunk):
+        n = min(chunk, numel - lo)
+        z = torch.arange(lo + 1, lo + n + 1, dtype=torch.int64, device=device)
+        z = z * golden + _i64(key)
+        z = (z ^ _lsr(z, 30)) * m1
+        z = (z ^ _lsr(z, 27)) * m2
+        z = z ^ _lsr(z, 31)
+        cell = _lsr(z, 48)
+        frac = (_lsr(z, 16) & 0xFFFFFFFF).to(torch.float64) * (1.0 / 4294967296.0)
+        a = table[cell]
+        b = table[cell + 1]
+        out[lo:lo + n] = a + (b - a) * frac
+    return out
+
+
 class RandomSource(WeightSource):
     """Seeded weights: matrices and biases N(0, std), norm gains 1 + N(0, std).
 
-    A tensor's values depend on (seed, name, device type) only, not on the order
-    of generation.  On a CUDA device the device's generator is used, so a model of
-    many billions of parameters is drawn in seconds."""
+    A tensor's values depend on (seed, name) only: not on the order of generation and
+    not on the device they are drawn on (``counter_normal``).  A model of many billions
+    of parameters is drawn on the GPU in seconds, and the same seed on the CPU gives a
+    plain implementation the same model without a folder in between."""
 
     def __init__(self, seed: int, std: float = 0.02, device: str = "cpu"):
         self.seed = int(seed)
@@ -98,15 +163,16 @@ class RandomSource(WeightSource):
     def fetch(self, decl):
         if decl.keep == "int32":
             return torch.zeros(decl.shape, dtype=torch.int32, device=self.device)
-        g = torch.Generator(device=self.device)
-        g.manual_seed(_name_seed(self.seed, decl.name))
         if decl.init == "zeros":
             return torch.zeros(decl.shape, dtype=torch.float32, device=self.device)
-        t = torch.randn(decl.shape, generator=g, dtype=torch.float32, device=self.device)
-        t.mul_(self.std)
+        numel = 1
+        for n in decl.shape:
+            numel *= int(n)
+        t = counter_normal(_name_seed(self.seed, decl.name), numel, self.device)
+        t = t * self.std          # in double; one rounding to fp32 below
         if decl.init == "gain":
-            t.add_(1.0)
-        return t
+            t = t + 1.0
+        return t.to(torch.float32).reshape(decl.shape)
 
 
 def check(decls: Sequence[TensorDecl], source: WeightSource, where: str = "weights") -> None:

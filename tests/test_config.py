@@ -163,3 +163,21 @@ def test_random_model_folder_states_layer_types(tmp_path, tiny_b):
     mine = ["sliding_attention", "full_attention", "sliding_attention"]
     write_random_model(dict(tiny_b, layer_types=mine), str(tmp_path / "n"), seed=0)
     assert json.loads((tmp_path / "n" / "config.json").read_text())["layer_types"] == mine
+
+
+def test_sizes_beyond_the_kernels_are_refused_when_the_model_is_built(tiny_a):
+    """Not at the first launch: the parts ask the kernel module for its limits while the
+    model is put together (no device needed for that)."""
+    import torch
+    from inferx_b200.kernels import ops
+    from inferx_b200.parts import BuildContext
+    from inferx_b200.parts.block import DecoderModel
+    ctx = BuildContext(dtype=torch.bfloat16, device=torch.device("cpu"), ops=ops)
+    _, spec = config_from_json(dict(tiny_a, num_experts=64, num_experts_per_tok=40))
+    with pytest.raises(ops.KernelError, match="40 experts per token exceed"):
+        DecoderModel(spec, ctx)
+    _, spec = config_from_json(dict(tiny_a, head_dim=1024))
+    with pytest.raises(ops.KernelError, match="head size 1024 exceeds"):
+        DecoderModel(spec, ctx)
+    _, spec = config_from_json(tiny_a)
+    assert len(DecoderModel(spec, ctx).blocks) == 2

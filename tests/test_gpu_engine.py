@@ -59,7 +59,7 @@ def test_repeated_prompt_shapes_are_captured_too(tmp_path, dtype):
     rows = mc.run_trace(sess, steps)
     assert len(rows) == 1 + 6 * 3
     ex = sess.executor
-    assert ex.graph_replays >= 4 and any(not isinstance(k[0], int) for k in ex._graphs)
+    assert ex.graph_replays >= 4 and ex._graphs.count(False) >= 1
     mc.compare(rows, ref, mc.bound_for(dtype, d, reqs), f"prompt graphs {dtype}")
 
 

@@ -92,7 +92,8 @@ def test_swiglu_part(dtype):
 def test_moe_part(dtype, renorm, shared, gated):
     ctx = _ctx(dtype)
     spec = MoeSpec(hidden=64, num_experts=6, top_k=3, expert_intermediate=40, renormalize=renorm,
-                   routed_scale=1.0, shared_intermediate=shared, shared_gated=gated)
+                   routed_scale=1.0, shared_gated=gated,
+                   shared=SwiGluSpec(hidden=64, intermediate=shared) if shared else None)
     part = build_part("feed_forward", spec, ctx, "mlp")
     w = _bind(part, ctx, std=0.15)
     cfg = {"num_experts": 6, "num_experts_per_tok": 3, "norm_topk_prob": renorm,
@@ -195,17 +196,25 @@ class RunningMeanMixer:
         return [StateNeed("sum", (self.spec.hidden,)), StateNeed("count", (1,))]
 
     def forward(self, x, step, cache):
+        # State is indexed with the device's copy of the slots, which a replayed step
+        # refreshes; the loop runs over the step's shape (tokens per sequence), which is
+        # the same for every replay.  Nothing here reads a device value on the host, so
+        # the step can be recorded into a CUDA graph.
+        slots = step.state_slot.long()
+        sums = cache.state["sum"].index_select(0, slots)          # [S, hidden]
+        counts = cache.state["count"].index_select(0, slots)      # [S, 1]
         out = torch.empty_like(x)
-        slots = step.state_slot.tolist()
+        last = []
         at = 0
         for s, n in enumerate(step.q_lens):
-            slot = slots[s]
-            run = torch.cumsum(x[at:at + n].float(), 0) + cache.state["sum"][slot]
-            cnt = cache.state["count"][slot] + torch.arange(1, n + 1, device=x.device)
+            run = torch.cumsum(x[at:at + n].float(), 0) + sums[s]
+            cnt = counts[s] + torch.arange(1, n + 1, device=x.device)
             out[at:at + n] = ((run / cnt[:, None]) @ self.w.float().T).to(x.dtype)
-            cache.state["sum"][slot] = run[-1]
-            cache.state["count"][slot] += n
+            last.append(run[-1])
             at += n
+        cache.state["sum"].index_copy_(0, slots, torch.stack(last))
+        taken = (step.cu_q[1:] - step.cu_q[:-1]).to(torch.float32)[:, None]
+        cache.state["count"].index_copy_(0, slots, counts + taken)
         return out
 
 
@@ -267,14 +276,24 @@ def _toy_plain(w, tokens, hidden):
     return n @ w["model.embed_tokens.weight"].T
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
+def _register_toy_state():
     register_part("mixer", "toy_running_mean", RunningMeanMixer)
     register_architecture(
         "ToyStateForCausalLM",
         lambda obj, where: SimpleNamespace(hidden=obj["hidden_size"], vocab=obj["vocab_size"],
                                            eos_token_ids=()),
         _toy_spec)
+
+
+def _unregister_toy_state():
+    unregister_part("mixer", "toy_running_mean")
+    arch_registry._ARCHITECTURES.pop("ToyStateForCausalLM", None)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype, graphs):
+    _register_toy_state()
     try:
         cfg = {"architectures": ["ToyStateForCausalLM"], "hidden_size": 32, "vocab_size": 97,
                "torch_dtype": "float32"}
@@ -289,15 +308,220 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
             lg = _toy_plain(w, toks, 32)
             for p in range(len(toks)):
                 ref[(rid, p)] = lg[p]
-        for kind in ("whole", "portions", "mixed"):
+        for kind in ("whole", "tail", "portions", "mixed"):
             steps = mc.TRACE_KINDS[kind](reqs)
-            sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=4, max_live=4)
+            sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=4, max_live=4,
+                                 use_graphs=graphs)
             rows = mc.run_trace(sess, steps)
             # a request that ended gave its slot back; the next one started from zero state
             mc.compare(rows, ref, 2e-5 if dtype == "float32" else 4e-2, f"toy/{kind}/{dtype}")
+            if graphs and kind == "tail":
+                # single-token steps repeat a shape: they were replayed from a recording,
+                # each replay with another request's slot in the device's index array
+                assert sess.executor.graph_replays >= 20
     finally:
-        unregister_part("mixer", "toy_running_mean")
-        arch_registry._ARCHITECTURES.pop("ToyStateForCausalLM", None)
+        _unregister_toy_state()
+
+
+def test_toy_state_is_rebuilt_after_preemption(tmp_path):
+    """Through the engine, with recorded steps (its default) and a pool so small that a
+    request is preempted: its pages and its slot are given back, and on re-admission
+    its state is recomputed from zero over all its tokens.  The tokens generated must be
+    those of a roomy run, and those of the plain restatement."""
+    from inferx_b200 import Engine, EngineConfig, Request, SamplingParams
+    _register_toy_state()
+    try:
+        cfg = {"architectures": ["ToyStateForCausalLM"], "hidden_size": 32, "vocab_size": 97,
+               "torch_dtype": "float32"}
+        d = str(tmp_path / "toy")
+        write_random_model(cfg, d, seed=4, std=0.2, dtype="float32")
+        _, w = plain.read_model_folder(d)
+        reqs = mc.make_requests({"vocab_size": 97}, [5, 9, 17], 3)
+
+        def run(pages):
+            eng = Engine.create(EngineConfig(model=d, dtype="float32", block_size=4,
+                                             max_num_seqs=3, num_gpu_blocks_override=pages,
+                                             max_model_len=64))
+            outs = eng.generate([Request(t, SamplingParams(max_tokens=10))
+                                 for t in reqs.values()])
+            eng.runtime.manager.check_invariants()
+            return [c.output_tokens for c in outs], eng.stats()
+
+        roomy, st0 = run(64)
+        tight, st1 = run(7)
+        assert st0["preemptions"] == 0 and st1["preemptions"] >= 1
+        assert st0["graph_replays"] > 0
+        assert tight == roomy
+        for toks, out in zip(reqs.values(), roomy):
+            seq = list(toks)
+            for t in out:
+                assert int(_toy_plain(w, seq, 32)[-1].argmax()) == t
+                seq.append(t)
+    finally:
+        _unregister_toy_state()
+
+
+# ---------------------------------------------------------------------------
+# a mixer that keeps ONE vector per token, over a window, and a block of another
+# arrangement: both defined here
+# ---------------------------------------------------------------------------
+@dataclass(frozen=True)
+class LatentWindowSpec:
+    hidden: int
+    latent: int
+    window: int
+    kind: str = "toy_latent_window"
+
+
+class LatentWindowMixer:
+    """out[t] = W_up . mean(c[max(0, t-W+1) .. t]) with c[t] = W_down . x[t]: one latent
+    vector per token in pages (a single-entry record kept in fp32, not a key and value
+    pair), of which only a window is read, so pages behind the window are given back."""
+
+    def __init__(self, spec, ctx, prefix):
+        self.spec, self.ctx, self.prefix = spec, ctx, prefix
+
+    def tensors(self):
+        s = self.spec
+        return [TensorDecl(f"{self.prefix}.down.weight", (s.latent, s.hidden)),
+                TensorDecl(f"{self.prefix}.up.weight", (s.hidden, s.latent))]
+
+    def bind(self, w):
+        self.down, self.up = w[f"{self.prefix}.down.weight"], w[f"{self.prefix}.up.weight"]
+
+    def cache_needs(self):
+        from inferx_b200.parts import PagedKvNeed
+        return [PagedKvNeed(kv_heads=1, head_dim=self.spec.latent, window=self.spec.window,
+                            entries=("latent",), dtype=torch.float32)]
+
+    def forward(self, x, step, cache):
+        group = step.groups[cache.group]
+        assert group.window == self.spec.window
+        store = cache.pages["latent"]                   # [pages, 1, page_size, latent] fp32
+        assert set(cache.pages) == {"latent"} and cache.k is None
+        ps, W = group.page_size, self.spec.window
+        flat = store.view(-1, self.spec.latent)         # row = page * page_size + offset
+        c = x.float() @ self.down.float().T
+        flat.index_copy_(0, group.slots.long(), c)
+        # every query gathers its window through the block table, on the device
+        pos = step.positions.long()
+        back = torch.arange(W, device=x.device)
+        key_pos = pos[:, None] - back[None, :]                       # [T, W]
+        valid = key_pos >= 0
+        key_pos = key_pos.clamp(min=0)
+        table = group.block_table.long()[step.seq_of_token.long()]   # [T, max_blocks]
+        page = torch.gather(table, 1, key_pos // ps)
+        rows = page * ps + key_pos % ps
+        # a page given back reads as -1: it must never be one a query still looks at
+        keys = flat[rows.clamp(min=0)] * (valid & (page >= 0))[..., None]
+        mean = keys.sum(1) / valid.sum(1, keepdim=True)
+        return (mean @ self.up.float().T).to(x.dtype)
+
+
+class ParallelBlock:
+    """Another arrangement of a layer's parts: x += mixer(norm(x)) + ffn(norm(x)), one
+    norm feeding both.  It takes the contribution still to be added from the block
+    before it and hands its own on, like the built-in arrangement."""
+
+    def __init__(self, spec, ctx, prefix):
+        self.norm = build_part("norm", spec.input_norm, ctx, f"{prefix}.{spec.input_norm_name}")
+        self.mixer = build_part("mixer", spec.mixer, ctx, f"{prefix}.{spec.mixer_name}")
+        self.ffn = build_part("feed_forward", spec.ffn, ctx, f"{prefix}.{spec.ffn_name}")
+
+    def parts(self):
+        return [self.norm, self.mixer, self.ffn]
+
+    def cache_needs(self):
+        return list(self.mixer.cache_needs())
+
+    def forward(self, resid, pending, step, cache):
+        if hasattr(pending, "materialize"):
+            pending = pending.materialize()
+        n = self.norm.forward(resid, pending)
+        return self.mixer.forward(n, step, cache) + self.ffn.forward(n, step)
+
+
+def _toy3_spec(cfg):
+    norm = RmsNormSpec(size=cfg.hidden, eps=1e-6)
+    ffn = SwiGluSpec(hidden=cfg.hidden, intermediate=24)
+    latent = LatentWindowSpec(hidden=cfg.hidden, latent=8, window=5)
+    attn = AttentionSpec(hidden=cfg.hidden, heads=2, kv_heads=2, head_dim=16, qkv_bias=False,
+                         scale=0.25, window=5,
+                         position=RopeSpec(head_dim=16, rotary_dim=16, theta=1e4))
+    layers = (
+        LayerSpec("model.layers.0", norm, latent, None, ffn, mixer_name="lat", kind="toy_parallel"),
+        # the same window as the latent layer: both live in one cache group and share page
+        # numbers although one keeps a latent vector and the other keys and values
+        LayerSpec("model.layers.1", norm, attn, norm, ffn),
+    )
+    return ModelSpec(architecture="ToyLatentForCausalLM", vocab_size=cfg.vocab, hidden=cfg.hidden,
+                     layers=layers, schedule=(RunEntry(0), RunEntry(1)), final_norm=norm,
+                     tied_head=True)
+
+
+def _toy3_plain(w, tokens, hidden):
+    x = w["model.embed_tokens.weight"][torch.tensor(tokens)]
+    T = len(tokens)
+    pos = torch.arange(T)
+    n = plain.rmsnorm(x, w["model.layers.0.input_layernorm.weight"], 1e-6)
+    c = n @ w["model.layers.0.lat.down.weight"].T
+    mix = torch.stack([c[max(0, t - 4):t + 1].mean(0) for t in range(T)])
+    x = x + mix @ w["model.layers.0.lat.up.weight"].T + plain.swiglu_mlp(w, "model.layers.0.mlp", n)
+    p = "model.layers.1.self_attn"
+    n = plain.rmsnorm(x, w["model.layers.1.input_layernorm.weight"], 1e-6)
+    q = (n @ w[f"{p}.q_proj.weight"].T).view(T, 2, 16)
+    k = (n @ w[f"{p}.k_proj.weight"].T).view(T, 2, 16)
+    v = (n @ w[f"{p}.v_proj.weight"].T).view(T, 2, 16)
+    o = plain.attention(plain.rope(q, pos, 1e4), plain.rope(k, pos, 1e4), v, 0.25, 5)
+    x = x + o.reshape(T, 32) @ w[f"{p}.o_proj.weight"].T
+    n = plain.rmsnorm(x, w["model.layers.1.post_attention_layernorm.weight"], 1e-6)
+    x = x + plain.swiglu_mlp(w, "model.layers.1.mlp", n)
+    n = plain.rmsnorm(x, w["model.norm.weight"], 1e-6)
+    return n @ w["model.embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_single_entry_paged_mixer_and_block_arrangement(tmp_path, dtype, graphs):
+    register_part("mixer", "toy_latent_window", LatentWindowMixer)
+    register_part("block", "toy_parallel", ParallelBlock)
+    register_architecture(
+        "ToyLatentForCausalLM",
+        lambda obj, where: SimpleNamespace(hidden=obj["hidden_size"], vocab=obj["vocab_size"],
+                                           eos_token_ids=()),
+        _toy3_spec)
+    try:
+        cfg = {"architectures": ["ToyLatentForCausalLM"], "hidden_size": 32, "vocab_size": 83,
+               "torch_dtype": "float32"}
+        d = str(tmp_path / "toy3")
+        write_random_model(cfg, d, seed=11, std=0.2,
+                           dtype="float32" if dtype == "float32" else "bfloat16")
+        _, w = plain.read_model_folder(d)
+        assert "model.layers.0.lat.down.weight" in w
+        assert "model.layers.0.post_attention_layernorm.weight" not in w
+        reqs = mc.make_requests({"vocab_size": 83}, [9, 41, 17, 5, 30], 6)
+        ref = {}
+        for rid, toks in reqs.items():
+            lg = _toy3_plain(w, toks, 32)
+            for p in range(len(toks)):
+                ref[(rid, p)] = lg[p]
+        for kind in ("whole", "tail", "portions", "mixed"):
+            steps = mc.TRACE_KINDS[kind](reqs)
+            sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=4, max_live=4,
+                                 use_graphs=graphs)
+            mgr = sess.manager
+            # one group (window 5) for both layers; the latent layer has one fp32 tensor
+            # per page, the attention layer a key and a value tensor in the run's type
+            assert [g.window for g in mgr.groups] == [5] and mgr.groups[0].layers == (0, 1)
+            st = sess.runtime.storage
+            assert list(st.paged[0]) == ["latent"] and st.paged[0]["latent"].dtype == torch.float32
+            assert sorted(st.paged[1]) == ["k", "v"]
+            rows = mc.run_trace(sess, steps)
+            mc.compare(rows, ref, 2e-5 if dtype == "float32" else 4e-2, f"toy3/{kind}/{dtype}")
+    finally:
+        unregister_part("mixer", "toy_latent_window")
+        unregister_part("block", "toy_parallel")
+        arch_registry._ARCHITECTURES.pop("ToyLatentForCausalLM", None)
 
 
 # ---------------------------------------------------------------------------

@@ -237,3 +237,35 @@ def test_windowed_groups_under_preemption_leave_nothing_behind():
     done, _ = run(s, c)
     assert len(done) == 5
     assert c.free_pages(0) == 8 and c.free_pages(1) == 8 and c.free_slots() == 8
+
+
+def test_recorded_step_shapes_stay_bounded():
+    """A serving run meets ever new (batch size, table width) shapes; the number of
+    recorded steps kept must not grow with them.  The least recently used goes."""
+    from inferx_b200.engine.executor import GraphCache
+    cache = GraphCache(decode_graphs=5, prompt_graphs=2)
+    recorded = 0
+    for width in (8, 16, 32, 64):
+        for batch in range(1, 40):
+            key = (batch, (width,), tuple(range(batch)))
+            for _ in range(3):
+                if cache.get(key) is None and cache.should_record(key, True):
+                    cache.put(key, object(), True)
+                    recorded += 1
+            assert cache.count(True) <= 5
+    assert recorded == 4 * 39 and cache.evictions == recorded - 5 and len(cache) == 5
+    # a shape is recorded at its second sighting (decode) or its third (prompts)
+    fresh = GraphCache()
+    assert not fresh.should_record("d", True) and fresh.should_record("d", True)
+    assert [fresh.should_record("p", False) for _ in range(3)] == [False, False, True]
+    # the one just used survives the next eviction
+    lru = GraphCache(decode_graphs=2)
+    lru.put("a", 1, True)
+    lru.put("b", 2, True)
+    assert lru.get("a") == 1
+    lru.put("c", 3, True)
+    assert lru.get("b") is None and lru.get("a") == 1 and lru.get("c") == 3
+    # prompt shapes have a bound of their own and do not push decode shapes out
+    for i in range(10):
+        lru.put(((i, 5), (8,), ()), i, False)
+    assert lru.count(False) == 4 and lru.count(True) == 2

@@ -137,6 +137,30 @@ def test_random_weights_depend_on_seed_and_name_only(tiny_b):
     assert abs(float(a.fetch(mat).std()) - 0.02) < 0.004
 
 
+def test_counter_generator_is_plain_integer_arithmetic():
+    """The generator restated with Python integers: splitmix64 of key + (i+1) * golden,
+    16 bits choose a cell of the inverse normal distribution, 32 bits a place in it.
+    Whoever draws element i alone, in any chunking, gets the same double."""
+    from statistics import NormalDist
+    from inferx_b200.weights.loader import counter_normal
+    key, mask = 0x1234_5678_9ABC_DEF1, (1 << 64) - 1
+    got = counter_normal(key, 5000, "cpu")
+    assert torch.equal(counter_normal(key, 5000, "cpu", chunk=13), got)
+    inv = NormalDist().inv_cdf
+    q = lambda j: inv(0.25 / 65536) if j == 0 else -inv(0.25 / 65536) if j == 65536 \
+        else inv(j / 65536)
+    for i in (0, 1, 77, 4999):
+        z = (key + (i + 1) * 0x9E3779B97F4A7C15) & mask
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+        z ^= z >> 31
+        cell, frac = z >> 48, ((z >> 16) & 0xFFFFFFFF) / 4294967296.0
+        assert got[i].item() == q(cell) + (q(cell + 1) - q(cell)) * frac
+    big = counter_normal(3, 1 << 20, "cpu")
+    assert abs(big.mean().item()) < 5e-3 and abs(big.std().item() - 1) < 5e-3
+    assert 0.0015 < (big.abs() > 3).double().mean().item() < 0.004     # 0.0027 for a normal
+
+
 def test_random_model_folder_names_and_dtypes(tmp_path, tiny_a, tiny_b):
     for cfg, n_expected in ((tiny_a, None), (tiny_b, None)):
         d = str(tmp_path / f"m{cfg['hidden_size']}")
