@@ -114,7 +114,7 @@ def _lsr(z: torch.Tensor, n: int) -> torch.Tensor:
     return (z >> n) & ((1 << (64 - n)) - 1)
 
 
-def counter_normal(key: int, numel: int, device, chunk: int = 1 << 24) -> torch.Tensor:
+def counter_normal(key: int, numel: int, device, chunk: int = 0) -> torch.Tensor:
     """``numel`` standard-normal fp64 values that depend on (key, index) only.
 
     Element i hashes the counter ``key + (i + 1) * golden`` with the splitmix64
@@ -124,6 +124,8 @@ def counter_normal(key: int, numel: int, device, chunk: int = 1 << 24) -> torch.
     double operations: the same bits on the CPU and on a CUDA device, in any order of
     generation, which a library's generator does not give."""
     table = _quantile_table(device)
+    if chunk <= 0:   # temporaries that stay in the CPU's caches; large launches on a GPU
+        chunk = 1 << 20 if torch.device(device).type == "cpu" else 1 << 24
     out = torch.empty(numel, dtype=torch.float64, device=device)
     golden, m1, m2 = _i64(0x9E3779B97F4A7C15), _i64(0xBF58476D1CE4E5B9), _i64(0x94D049BB133111EB)
     for lo in range(0, numel, chunk):

@@ -163,6 +163,65 @@ def test_temperature_sampling_is_seeded_and_varied(tmp_path):
     assert outs[1].output_tokens == a
 
 
+def test_temperature_workload_draws_what_the_plain_sampler_draws(tmp_path):
+    """Four requests with prompts of 1, 6, 13 and 31 tokens, portions of 7, pages of 8,
+    12 tokens each at temperature 0.7, each request with a seed of its own, in 32-bit:
+    every token the engine drew is the one the plain sampler draws from the plain
+    model's logits with the row's seed (seed ^ golden * tokens so far,
+    src/scheduler/scheduler.cc:613-615).  A draw may differ only where the uniform
+    number falls on the edge between two tokens' shares, within rounding."""
+    cfg = TINY_B
+    d = mc.make_model_dir(cfg, tmp_path / "m", 1)
+    reqs = mc.make_requests(cfg, [1, 6, 13, 31], 1)
+    eng = Engine.create(EngineConfig(model=d, dtype="float32", block_size=8, max_num_seqs=4,
+                                     num_gpu_blocks_override=40, prefill_chunk=7,
+                                     max_model_len=64))
+    seeds = [11, 22, 33, 44]
+    outs = eng.generate([Request(t, SamplingParams(max_tokens=12, temperature=0.7, seed=sd))
+                         for t, sd in zip(reqs.values(), seeds)])
+    pcfg, w = plain.read_model_folder(d)
+    mask = (1 << 64) - 1
+    on_edge = 0
+    for toks, sd, c in zip(reqs.values(), seeds, outs):
+        assert len(c.output_tokens) == 12
+        seq = list(toks)
+        lg = plain.forward(pcfg, w, seq + c.output_tokens)
+        for j, got in enumerate(c.output_tokens):
+            n_before = len(toks) + j
+            row_seed = (sd ^ ((0x9E3779B97F4A7C15 * n_before) & mask)) & mask
+            want, cdf, target = plain.sample_temperature(lg[n_before - 1], 0.7, row_seed)
+            if got != want:
+                # only on an edge: the target within 1e-5 of the total of the boundary
+                edge = min(abs(float(cdf[min(got, want)]) - target),
+                           abs(float(cdf[max(got, want) - 1]) - target))
+                assert abs(got - want) == 1 and edge <= 1e-5 * float(cdf[-1]), (j, got, want)
+                on_edge += 1
+    assert on_edge <= 1
+    assert len({tuple(c.output_tokens) for c in outs}) == 4
+
+
+def test_a_wait_that_ran_out_is_reported(tmp_path):
+    """Kernels with bounded waits write a code into a status word instead of hanging.
+    The word is written from the host here (no kernel is made to wait): reading it must
+    raise and name the kernel and the role, the word must be cleared, and generation must
+    surface the error rather than return tokens computed from an invalid step."""
+    from inferx_b200.kernels import ops
+    st = ops._tc_status(torch.device("cuda:0"))
+    st.fill_(22)
+    with pytest.raises(ops.KernelError, match=r"paged_attention_prefill \(tcgen05 form\): the MMA "
+                                              r"issuer waited past its limit \(status 22\)"):
+        ops.check_async_errors()
+    assert int(st.item()) == 0
+    ops.check_async_errors()            # cleared: nothing to report
+    d = mc.make_model_dir(TINY_A, tmp_path / "m", 0)
+    eng = Engine.create(EngineConfig(model=d, dtype="float32", block_size=4,
+                                     num_gpu_blocks_override=16, max_model_len=32))
+    st.fill_(2)
+    with pytest.raises(ops.KernelError, match="grouped_gemm_tc: the MMA issuer"):
+        eng.generate([Request([1, 2, 3], SamplingParams(max_tokens=2))])
+    assert int(st.item()) == 0
+
+
 def test_command_line(tmp_path):
     cfg = dict(TINY_A, eos_token_id=5)
     d = mc.make_model_dir(cfg, tmp_path / "m", 0)

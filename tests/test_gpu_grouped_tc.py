@@ -38,11 +38,13 @@ def test_grouped_gemm_tc(T, H, I, E, k):
     act = ops.grouped_gemm_tc(xg, off.cuda(), wgu.cuda(), True)
     ops.check_async_errors()
     ract = host_ops.grouped_gate_up_swiglu(x, rows, off, wgu)
-    torch.testing.assert_close(act.cpu().float(), ract.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(act.cpu().float(), ract.float(), rtol=2.0 ** -7,
+                               atol=2.0 ** -7 * float(ract.float().abs().max()))
     y = ops.grouped_gemm_tc(ract.cuda(), off.cuda(), wd.cuda(), False)
     ops.check_async_errors()
     ry = host_ops.grouped_down(ract, off, wd)
-    torch.testing.assert_close(y.cpu().float(), ry.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(y.cpu().float(), ry.float(), rtol=2.0 ** -7,
+                               atol=2.0 ** -7 * float(ry.float().abs().max()))
 
 
 def test_grouped_gemm_tc_empty_experts_and_one_hot_rows():

@@ -11,6 +11,7 @@ import pytest
 import torch
 
 import model_cases as mc
+import plain_qwen2_moe as plain
 import traces
 from conftest import ROOT, TINY_A, TINY_B, TINY_B_LISTED
 from inferx_b200.engine.replay import ReplaySession
@@ -158,35 +159,118 @@ def test_head_size_64_over_page_sizes(tmp_path):
             print(f"hd64/page{page}/{kind}: worst relative error {worst:.3e} (bound {bound:.3e})")
 
 
-def test_grouped_query_heads_at_width(tmp_path):
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_grouped_query_heads_at_width(tmp_path, dtype):
     """Seven query heads per KV head, head size 128, top-8 routing (the shape family of
     the larger Qwen2-MoE checkpoints, scaled down in width): the tensor-core attention
-    kernels pack the seven heads of a group into one tile."""
-    d = mc.make_model_dir(GQA, tmp_path / "m", 4, dtype="bfloat16")
+    kernels pack the seven heads of a group into one tile; in 32-bit the split-KV kernel
+    of the single-token steps is a different one from the tiny configurations'."""
+    store = "float32" if dtype == "float32" else "bfloat16"
+    d = mc.make_model_dir(GQA, tmp_path / "m", 4, dtype=store)
     reqs = mc.make_requests(GQA, [200, 75, 33], 4)
     ref = mc.reference_rows(d, reqs)
-    bound = mc.bf16_bound(d, reqs)
+    bound = mc.bound_for(dtype, d, reqs)
     for kind in ("tail", "mixed"):
         steps = mc.TRACE_KINDS[kind](reqs)
-        sess = ReplaySession(d, "bfloat16", traces.peak_tokens(steps), page_size=16, max_live=4,
+        sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=16, max_live=4,
                              use_graphs=(kind == "tail"))
         rows = mc.run_trace(sess, steps)
-        worst = mc.compare(rows, ref, bound, f"gqa/{kind}")
-        print(f"gqa/{kind}: worst relative error {worst:.3e} (bound {bound:.3e})")
+        worst = mc.compare(rows, ref, bound, f"gqa/{kind}/{dtype}")
+        print(f"gqa/{kind}/{dtype}: worst relative error {worst:.3e} (bound {bound:.3e})")
 
 
-def test_layer_sizes_of_the_benchmark_model(tmp_path):
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_layer_sizes_of_the_benchmark_model(tmp_path, dtype):
     """Two layers at the widths the benchmark runs (hidden 2048, 16 heads of 128, 60
     experts of 1408, shared 5632, dense 5632, a 96-token window): the tuned kernels see
-    their real shapes, prompt-sized and decode-sized, against the plain model."""
-    d = mc.make_model_dir(MID, tmp_path / "m", 3, dtype="bfloat16")
+    their real shapes, prompt-sized and decode-sized, against the plain model; in 32-bit
+    through all four ways of cutting the same requests, at the 32-bit bound."""
+    store = "float32" if dtype == "float32" else "bfloat16"
+    d = mc.make_model_dir(MID, tmp_path / "m", 3, dtype=store)
     reqs = mc.make_requests(MID, [330, 150, 40], 3)
     ref = mc.reference_rows(d, reqs)
-    bound = mc.bf16_bound(d, reqs)
-    for kind in ("tail", "mixed"):
+    bound = mc.bound_for(dtype, d, reqs)
+    for kind in (("tail", "mixed") if dtype == "bfloat16" else tuple(mc.TRACE_KINDS)):
         steps = mc.TRACE_KINDS[kind](reqs)
-        sess = ReplaySession(d, "bfloat16", traces.peak_tokens(steps), page_size=16, max_live=4,
+        sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=16, max_live=4,
                              use_graphs=True)
         rows = mc.run_trace(sess, steps)
-        worst = mc.compare(rows, ref, bound, f"mid/{kind}")
-        print(f"mid/{kind}: worst relative error {worst:.3e}")
+        worst = mc.compare(rows, ref, bound, f"mid/{kind}/{dtype}")
+        print(f"mid/{kind}/{dtype}: worst relative error {worst:.3e}")
+
+
+LONG = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "num_hidden_layers": 2, "hidden_size": 1024, "num_attention_heads": 8,
+    "num_key_value_heads": 2, "head_dim": 128, "num_experts": 8, "num_experts_per_tok": 2,
+    "moe_intermediate_size": 128, "shared_expert_intermediate_size": 256,
+    "decoder_sparse_step": 1, "mlp_only_layers": [], "norm_topk_prob": True,
+    "vocab_size": 300, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "use_sliding_window": True, "sliding_window": 3000, "max_window_layers": 1,
+    "tie_word_embeddings": True, "torch_dtype": "bfloat16",
+}
+
+
+def far_key_stands_out(name, t):
+    """With some 8,000 random keys every attention weight is about 1/8,000 and a kernel
+    that skipped a run of keys would hardly move the logits; sharper queries and keys
+    let single far keys carry weight."""
+    if name.endswith(("q_proj.weight", "k_proj.weight")):
+        return t * 2.5
+    if name.endswith("mlp.gate.weight"):
+        return t * 2.0
+    return t
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_long_context_inside_a_trace(tmp_path, dtype):
+    """Contexts at which both attention kernels cut a query's keys into runs that are
+    merged afterwards (a 512-token portion after 4,096 cached tokens; single tokens
+    beyond 8,192), inside a replayed trace with a second request decoding beside the
+    long one, one layer with all keys and one with a 3,000-token window whose pages are
+    given back as it moves: against the plain model's one pass over the whole
+    sequence."""
+    from inferx_b200.weights.random_model import write_random_model
+    store = "float32" if dtype == "float32" else "bfloat16"
+    d = str(tmp_path / "m")
+    write_random_model(LONG, d, seed=12, dtype=store, adjust=far_key_stands_out)
+    reqs = mc.make_requests(LONG, [8260, 90], 12)
+    big, small = reqs["r0"], reqs["r1"]
+    cfg, w = plain.read_model_folder(d)
+    ref_big = plain.forward(cfg, w, big)
+    ref_small = plain.forward(cfg, w, small)
+    ref = {("r0", p): ref_big[p] for p in range(len(big))}
+    ref.update({("r1", p): ref_small[p] for p in range(len(small))})
+    steps = [
+        {"entries": [{"id": "r0", "tokens": big[:4096], "want": [0, 2047, 4095]}]},
+        {"entries": [{"id": "r0", "tokens": big[4096:4608], "want": [0, 255, 511]},
+                     {"id": "r1", "tokens": small[:40], "want": [39]}]},
+        {"entries": [{"id": "r0", "tokens": big[4608:8200], "want": [0, 3591]},
+                     {"id": "r1", "tokens": [small[40]], "want": [0]}]},
+    ]
+    for i in range(60):     # single tokens at 8,200 and beyond, beside the short request
+        entries = [{"id": "r0", "tokens": [big[8200 + i]], "want": [0]}]
+        if 41 + i < len(small):
+            entries.append({"id": "r1", "tokens": [small[41 + i]], "want": [0]})
+        steps.append({"entries": entries})
+    for n, st in enumerate(steps):
+        st["step"] = n
+        st.setdefault("end", [])
+    steps[-1]["end"] = ["r0"]
+    steps[3 + len(small) - 42]["end"] = ["r1"]     # the step that brings r1's last token
+    sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=16, max_live=2,
+                         use_graphs=True)
+    outs = []
+    for st in steps:
+        lg = sess.run_step(st)
+        outs.append(None if lg is None else lg.detach().float().cpu())
+    sess.executor.poll_errors()
+    sess.manager.check_invariants()
+    rows = traces.collect(steps, outs)
+    if dtype == "float32":
+        bound = 2e-5
+    else:
+        a = plain.forward(cfg, w, big[:2100], plain.round_bf16)
+        bound = max(5e-3, 3.0 * float((a - ref_big[:2100]).abs().max()) / float(ref_big.abs().max()))
+    worst = mc.compare(rows, ref, bound, f"long/{dtype}")
+    print(f"long/{dtype}: worst relative error {worst:.3e} (bound {bound:.3e})")

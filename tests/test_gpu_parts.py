@@ -648,3 +648,36 @@ def test_toy_position_encoding_and_routed_feed_forward(tmp_path, dtype):
         unregister_part("position", "toy_learned_offset")
         unregister_part("feed_forward", "toy_parity_routed")
         arch_registry._ARCHITECTURES.pop("ToyRoutedForCausalLM", None)
+
+
+# ---------------------------------------------------------------------------
+# random weights: the same numbers wherever they are drawn
+# ---------------------------------------------------------------------------
+def test_random_weights_are_the_same_on_cpu_and_device():
+    decls = [TensorDecl("model.layers.3.mlp.experts.7.up_proj.weight", (130, 257)),
+             TensorDecl("model.norm.weight", (1000,), keep="float32", init="gain"),
+             TensorDecl("a.bias", (77,), keep="float32", init="bias")]
+    host, dev = RandomSource(9, std=0.02, device="cpu"), RandomSource(9, std=0.02, device="cuda")
+    for d in decls:
+        a, b = host.fetch(d), dev.fetch(d)
+        assert b.is_cuda and torch.equal(a, b.cpu()), d.name
+
+
+def test_model_drawn_on_the_device_against_plain_model_drawn_on_the_host():
+    """No folder in between: the engine draws its weights on the GPU from (seed, name),
+    the plain model draws the same tensors on the CPU, and their logits agree."""
+    from conftest import TINY_B
+    from inferx_b200.engine import Runtime, load_model
+    from inferx_b200.weights.random_model import declared_tensors
+    cfg = dict(TINY_B)
+    _, model = load_model(dtype="float32", device="cuda", config_json=cfg,
+                          source=RandomSource(21, std=0.05, device="cuda"))
+    host = RandomSource(21, std=0.05, device="cpu")
+    w = {d.name: host.fetch(d) for d in declared_tensors(cfg)}
+    toks = mc.make_requests(cfg, [37], 3)["r0"]
+    rt = Runtime(model, page_size=8, num_pages=8, max_slots=1)
+    rt.manager.open("r")
+    assert rt.manager.reserve("r", len(toks))
+    got = rt.executor.step([StepEntry("r", toks, list(range(len(toks))))]).cpu()
+    ref = plain.forward(cfg, w, toks)
+    assert float((got - ref).abs().max()) <= 2e-5 * float(ref.abs().max())

@@ -48,22 +48,58 @@ def _call_noalloc(lib, q, kc, vc, bt, kv_len, max_kv, window, scale):
     return rc, out
 
 
+def _plain_attention(q, kc, vc, bt, kv_len, window, scale):
+    """The fp32 statement of the same attention (tests/host_ops.py), on the CPU."""
+    import host_ops
+    S = q.shape[0]
+    return host_ops.paged_attention_generic(
+        q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), torch.arange(S, dtype=torch.int32),
+        (kv_len.cpu() - 1).to(torch.int32), window, scale).float()
+
+
 def test_noalloc_entry_matches_ordinary_entry_twice():
     from inferx_b200.kernels import library, ops
     lib = library.load()
     # first call on this device also does the one-time address look-up
-    shapes = [(11, 3, 8, 2, 128, 16, [700, 33, 1500]), (12, 2, 4, 4, 64, 8, [2049, 5])]
-    for seed, S, heads, kvh, hd, page, lens in shapes:
+    shapes = [(11, 3, 8, 2, 128, 16, [700, 33, 1500], 0), (12, 2, 4, 4, 64, 8, [2049, 5], 0),
+              (13, 2, 6, 2, 128, 16, [900, 300], 130)]          # the last with a window
+    for seed, S, heads, kvh, hd, page, lens, window in shapes:
         q, kc, vc, bt, kv_len = _case(seed, S, heads, kvh, hd, page, lens)
         scale = 1.0 / math.sqrt(hd)
-        ref = ops.paged_attention_decode(q, kc, vc, bt, kv_len, max(lens), 0, scale)
+        # the ordinary entry of the same kernel form (keys fed by cp.async, three blocks a
+        # multiprocessor decide the number of splits), and the plain fp32 statement
+        ref = ops.paged_attention_decode(q, kc, vc, bt, kv_len, max(lens), window, scale,
+                                         kernel="mma")
+        plain = _plain_attention(q, kc, vc, bt, kv_len, window, scale)
+        bound = 2.0 ** -7 * float(plain.abs().max())
         for _call in range(2):      # the second call finds the first one's leftovers
-            rc, out = _call_noalloc(lib, q, kc, vc, bt, kv_len, max(lens), 0, scale)
+            rc, out = _call_noalloc(lib, q, kc, vc, bt, kv_len, max(lens), window, scale)
             assert rc == 0
             torch.cuda.synchronize()
-            torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
-            # the same kernels and the same split count: the two entries agree to the bit
+            torch.testing.assert_close(out.float().cpu(), plain, rtol=2.0 ** -7, atol=bound)
+            # the same kernel and the same split count: the two entries agree to the bit
             assert torch.equal(out, ref)
+
+
+def test_noalloc_entry_without_splits_leaves_the_scratch_alone():
+    """Contexts so short that a block takes all keys of its (sequence, head group) pair:
+    nothing is written to the built-in array, the result comes straight from the
+    attention kernel."""
+    from inferx_b200.kernels import library, ops
+    lib = library.load()
+    S, heads, kvh, hd, page = 40, 16, 16, 64, 16
+    lens = [30 + 2 * i for i in range(S)]
+    assert lib.ix_attn_decode_splits(S, heads, kvh, max(lens)) == 1
+    q, kc, vc, bt, kv_len = _case(21, S, heads, kvh, hd, page, lens)
+    scale = 1.0 / math.sqrt(hd)
+    rc, out = _call_noalloc(lib, q, kc, vc, bt, kv_len, max(lens), 0, scale)
+    assert rc == 0
+    torch.cuda.synchronize()
+    plain = _plain_attention(q, kc, vc, bt, kv_len, 0, scale)
+    torch.testing.assert_close(out.float().cpu(), plain, rtol=2.0 ** -7,
+                               atol=2.0 ** -7 * float(plain.abs().max()))
+    assert torch.equal(out, ops.paged_attention_decode(q, kc, vc, bt, kv_len, max(lens), 0,
+                                                       scale, kernel="mma"))
 
 
 def test_noalloc_entry_refuses_what_does_not_fit():
