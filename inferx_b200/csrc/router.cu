@@ -367,11 +367,11 @@ IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, i
 // walks the assignment list with ballots, so the order inside an expert is the
 // assignment order and no atomics are involved.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024)
-moe_dispatch_kernel(const int* __restrict__ topk_idx, int A, int E, int k,
-                    int* __restrict__ offsets, int* __restrict__ rows, int* __restrict__ dest) {
-  extern __shared__ int counts[];  // [E + 1]
-  IX_PDL_WAIT();
+// `topk_idx` may be in shared or global memory; `counts` is [E + 1] ints of shared memory.
+__device__ __forceinline__ void dispatch_in_block(const int* topk_idx, int A, int E, int k,
+                                                  int* __restrict__ offsets,
+                                                  int* __restrict__ rows, int* __restrict__ dest,
+                                                  int* counts) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nwarps = blockDim.x >> 5;
   for (int e = warp; e < E; e += nwarps) {
@@ -384,16 +384,27 @@ moe_dispatch_kernel(const int* __restrict__ topk_idx, int A, int E, int k,
     if (lane == 0) counts[e] = c;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (warp == 0) {   // exclusive prefix sum over the experts, 32 at a time
     int run = 0;
-    for (int e = 0; e < E; ++e) {
-      const int c = counts[e];
-      counts[e] = run;
-      offsets[e] = run;
-      run += c;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int c = e < E ? counts[e] : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (e < E) {
+        counts[e] = run + incl - c;
+        offsets[e] = run + incl - c;
+      }
+      run += __shfl_sync(0xffffffffu, incl, 31);
     }
-    counts[E] = run;
-    offsets[E] = run;
+    if (lane == 0) {
+      counts[E] = run;
+      offsets[E] = run;
+    }
   }
   __syncthreads();
   for (int e = warp; e < E; e += nwarps) {
@@ -410,6 +421,14 @@ moe_dispatch_kernel(const int* __restrict__ topk_idx, int A, int E, int k,
       base += __popc(mask);
     }
   }
+}
+
+__global__ void __launch_bounds__(1024)
+moe_dispatch_kernel(const int* __restrict__ topk_idx, int A, int E, int k,
+                    int* __restrict__ offsets, int* __restrict__ rows, int* __restrict__ dest) {
+  extern __shared__ int counts[];  // [E + 1]
+  IX_PDL_WAIT();
+  dispatch_in_block(topk_idx, A, E, k, offsets, rows, dest, counts);
 }
 
 // ---------------------------------------------------------------------------

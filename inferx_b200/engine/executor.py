@@ -355,7 +355,9 @@ class Executor:
             dev.copy_(host, non_blocking=True)
             ctx, rows = self._context(dev, lay, static=True)
             torch.cuda.current_stream(self.device).synchronize()
-            if self._graph_pool is None:
+            if self._graph_pool is None or len(self._graphs) == 0:
+                # a pool lives as long as a graph recorded into it: with none left, the
+                # old handle names nothing
                 self._graph_pool = torch.cuda.graph_pool_handle()
             graph = torch.cuda.CUDAGraph()
             # One memory pool for all recorded steps: they run one after the other, so

@@ -330,6 +330,55 @@ def qkv_rope_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: 
     return (q, k, v) if want_dense_kv else q
 
 
+USE_FUSED_QKV = True
+
+
+def qkv_project_applies(x: torch.Tensor, w: torch.Tensor, heads: int, kv_heads: int,
+                        head_dim: int, rotary_dim: int) -> bool:
+    """Whether ``qkv_project_rope_append`` takes this step: bfloat16, a few tokens, a full
+    rotation or none."""
+    return bool(USE_FUSED_QKV and x.is_cuda and x.dtype == torch.bfloat16
+                and w.dtype == torch.bfloat16 and x.is_contiguous()
+                and _lib().ix_qkv_project_rope_applies(x.shape[0], x.shape[1], heads, kv_heads,
+                                                       head_dim, rotary_dim))
+
+
+def qkv_project_rope_append(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
+                            positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                            rotary_dim: int, heads: int, kv_heads: int, head_dim: int,
+                            k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor):
+    """For a step of a few tokens: q = rotate(x . Wq^T + bq) returned as [T, heads, hd],
+    rotate(x . Wk^T + bk) and x . Wv^T + bv written into the cache pages at ``slots``, in one
+    launch (``linear`` followed by ``qkv_rope_append`` otherwise)."""
+    _chk("x", x, torch.bfloat16)
+    _chk("w", w, torch.bfloat16)
+    _chk("bias", bias, torch.float32, optional=True)
+    _chk("positions", positions, torch.int32)
+    _chk("inv_freq", inv_freq, torch.float32, optional=True)
+    _chk("slots", slots, torch.int32)
+    _chk("k_cache", k_cache, torch.bfloat16)
+    _chk("v_cache", v_cache, torch.bfloat16)
+    T, K = x.shape
+    width = (heads + 2 * kv_heads) * head_dim
+    if w.shape != (width, K) or (bias is not None and bias.numel() != width):
+        raise KernelError("qkv_project_rope_append: weight or bias does not match the heads")
+    P, ckv, page_size, chd = k_cache.shape
+    if ckv != kv_heads or chd != head_dim or v_cache.shape != k_cache.shape:
+        raise KernelError("qkv_project_rope_append: cache geometry does not match the heads")
+    if rotary_dim and (inv_freq is None or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("qkv_project_rope_append: inv_freq must have rotary_dim/2 entries")
+    if positions.numel() != T or slots.numel() != T:
+        raise KernelError("qkv_project_rope_append: one position and one slot per token")
+    q = torch.empty((T, heads, head_dim), dtype=torch.bfloat16, device=x.device)
+    code = _lib().ix_qkv_project_rope_append(
+        _ptr(x), _ptr(w), _ptr(bias), _ptr(positions), _ptr(inv_freq), rotary_dim, _ptr(slots),
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), page_size, T, K, heads, kv_heads, head_dim,
+        _stream())
+    _check(code, "qkv_project_rope_append")
+    _count()
+    return q
+
+
 def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                             block_table: torch.Tensor, seq_of_token: torch.Tensor,
                             positions: torch.Tensor, window: int, scale: float):

@@ -69,11 +69,21 @@ class AttentionMixer:
     def forward(self, x, step, cache):
         s, ops = self.spec, self.ctx.ops
         group = step.groups[cache.group]
-        qkv = ops.linear(x, self.qkv_w)
         inv_freq, rot = (None, 0)
         if self.position is not None:
             inv_freq, rot = self.position.rotary_table()
         custom = getattr(self.position, "apply", None)
+        fused = getattr(ops, "qkv_project_applies", None)
+        if custom is None and cache.writes and fused is not None and fused(
+                x, self.qkv_w, s.heads, s.kv_heads, s.head_dim, rot):
+            # a few tokens: projection, bias, rotation and cache write in one kernel
+            q = ops.qkv_project_rope_append(
+                x, self.qkv_w, self.qkv_b, step.positions, inv_freq, rot, s.heads, s.kv_heads,
+                s.head_dim, cache.k, cache.v, group.slots)
+            attn = ops.paged_attention(q, cache.k, cache.v, group.block_table, step, s.window,
+                                       s.scale)
+            return ops.linear(attn.view(step.num_tokens, s.heads * s.head_dim), self.o_w)
+        qkv = ops.linear(x, self.qkv_w)
         if custom is None:
             q = ops.qkv_rope_append(
                 qkv, self.qkv_b, step.positions, inv_freq, rot, s.heads, s.kv_heads, s.head_dim,

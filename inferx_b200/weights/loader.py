@@ -170,11 +170,35 @@ class RandomSource(WeightSource):
         numel = 1
         for n in decl.shape:
             numel *= int(n)
-        t = counter_normal(_name_seed(self.seed, decl.name), numel, self.device)
+        key = _name_seed(self.seed, decl.name)
+        if self.device.type == "cuda":
+            # one kernel launch that does the same steps (csrc/random_weights.cu)
+            return self._fetch_on_device(key, numel, decl)
+        t = counter_normal(key, numel, self.device)
         t = t * self.std          # in double; one rounding to fp32 below
         if decl.init == "gain":
             t = t + 1.0
         return t.to(torch.float32).reshape(decl.shape)
+
+
+def _device_fetch(self, key: int, numel: int, decl: TensorDecl) -> torch.Tensor:
+    import ctypes
+    from ..kernels import library
+    lib = library.load()
+    table = _quantile_table(self.device)
+    out = torch.empty(decl.shape, dtype=torch.float32, device=self.device)
+    with torch.cuda.device(self.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        code = lib.ix_counter_normal(
+            ctypes.c_uint64(key), ctypes.c_longlong(numel), ctypes.c_void_p(table.data_ptr()),
+            ctypes.c_double(self.std), ctypes.c_double(1.0), 1 if decl.init == "gain" else 0,
+            ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(stream))
+    if code != 0:
+        raise RuntimeError(f"drawing '{decl.name}' on the device failed (code {code})")
+    return out
+
+
+RandomSource._fetch_on_device = _device_fetch
 
 
 def check(decls: Sequence[TensorDecl], source: WeightSource, where: str = "weights") -> None:

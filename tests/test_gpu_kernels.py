@@ -666,3 +666,59 @@ def test_prefill_attention_window_edge_and_far_key():
             out = ops.paged_attention_prefill(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(),
                                               cu_q.cuda(), q_pos0.cuda(), window, 1.0, kernel=form)
             assert (out[qrow, 0, 0].item() > 0.9) == expect, (form, window, which, qrow)
+
+
+@pytest.mark.parametrize("T,K,heads,kvh,hd,rot,bias,page", [
+    (1, 2048, 16, 16, 128, 128, True, 16), (8, 2048, 16, 16, 128, 128, True, 16),
+    (16, 3584, 28, 4, 128, 128, True, 16), (5, 200, 3, 1, 64, 64, False, 8),
+    (9, 96, 2, 2, 32, 0, True, 4), (13, 1032, 7, 7, 96, 96, True, 12)])
+def test_qkv_projection_with_rotation_and_cache_write_in_one_launch(T, K, heads, kvh, hd, rot,
+                                                                    bias, page):
+    """The fused kernel of few-token steps against the two kernels it replaces (the same
+    bits: the projection is rounded to bfloat16 where the tensor between them would be)
+    and against the plain statement."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + K)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    width = (heads + 2 * kvh) * hd
+    w = (torch.randn(width, K, generator=g) * (1.0 / math.sqrt(K))).to(torch.bfloat16)
+    b = torch.randn(width, generator=g) * 0.3 if bias else None
+    positions = torch.randint(0, 5000, (T,), generator=g).to(torch.int32)
+    inv = (10000.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / max(rot, 1))).float() \
+        if rot else None
+    pages = T + 3
+    slots = (torch.randperm(pages * page, generator=g)[:T]).to(torch.int32)
+    kc = torch.randn(pages, kvh, page, hd, generator=g).to(torch.bfloat16)
+    vc = torch.randn(pages, kvh, page, hd, generator=g).to(torch.bfloat16)
+    assert ops.qkv_project_applies(x.cuda(), w.cuda(), heads, kvh, hd, rot)
+    kc1, vc1 = kc.cuda(), vc.cuda()
+    launched = ops.LAUNCHES[0]
+    q1 = ops.qkv_project_rope_append(x.cuda(), w.cuda(), None if b is None else b.cuda(),
+                                     positions.cuda(), None if inv is None else inv.cuda(), rot,
+                                     heads, kvh, hd, kc1, vc1, slots.cuda())
+    assert ops.LAUNCHES[0] - launched == 1
+    # the two kernels it replaces
+    kc2, vc2 = kc.cuda(), vc.cuda()
+    qkv = ops.linear(x.cuda(), w.cuda())
+    q2 = ops.qkv_rope_append(qkv, None if b is None else b.cuda(), positions.cuda(),
+                             None if inv is None else inv.cuda(), rot, heads, kvh, hd, kc2, vc2,
+                             slots.cuda())
+    # the plain statement, from the plain product
+    kc3, vc3 = kc.clone(), vc.clone()
+    q3, _, _ = host_ops.qkv_rope_append(host_ops.linear(x, w), b, positions, inv, rot, heads, kvh,
+                                        hd, kc3, vc3, slots, want_dense_kv=True)
+    _close(q1.cpu(), q3, torch.bfloat16)
+    _close(kc1.cpu(), kc3, torch.bfloat16)
+    _close(vc1.cpu(), vc3, torch.bfloat16)
+    # rows of the cache that no slot names are untouched
+    untouched = torch.ones(pages * page, dtype=torch.bool)
+    untouched[slots.long()] = False
+    flat = lambda c: c.permute(0, 2, 1, 3).reshape(pages * page, kvh * hd)
+    assert torch.equal(flat(kc1.cpu())[untouched], flat(kc)[untouched])
+    assert torch.equal(flat(vc1.cpu())[untouched], flat(vc)[untouched])
+    # against the separate kernels: the same sums in the same order when both split K the
+    # same way; otherwise equal within one rounding of the projection
+    same = (q1 == q2).float().mean().item()
+    assert same > 0.98, same
+    _close(q1.cpu(), q2.cpu(), torch.bfloat16)
+    _close(kc1.cpu(), kc2.cpu(), torch.bfloat16)
