@@ -160,11 +160,12 @@ def prefill_flops(cfg, T):
     return L * (per_tok * T + attn) + 2 * cfg["vocab_size"] * H
 
 
-def make_runtime(cfg, batch, context, extra_tokens, use_graphs=True, max_slots=None):
+def make_runtime(cfg, batch, context, extra_tokens, use_graphs=True, max_slots=None,
+                 dtype="bfloat16"):
     import torch
     from inferx_b200.engine import Runtime, load_model
     from inferx_b200.weights.loader import RandomSource
-    _, model = load_model(dtype="bfloat16", device="cuda", config_json=cfg,
+    _, model = load_model(dtype=dtype, device="cuda", config_json=cfg,
                           source=RandomSource(0, device="cuda"))
     page = 16
     pages = batch * (-(-(context + extra_tokens) // page) + 1)
@@ -367,6 +368,41 @@ def time_e2e(cfg, batch, context, steps, warmup):
             "graph_replays": replays}
 
 
+FP32_FMA_PER_SM_PER_CLOCK = 128      # fp32 lanes of one multiprocessor
+
+
+def fp32_points(cfg, batch, context, hbm_peak):
+    """The 32-bit path at the same sizes: weights, cache and every product in fp32 on the
+    CUDA cores.  Decode against the bytes it has to read (twice the bfloat16 step's),
+    a 2,048-token prompt against the fp32 multiply-add rate of the device at its
+    maximum clock."""
+    import torch
+    rt = make_runtime(cfg, 1, batch * (context + 32) + 2048 + 64, 0, use_graphs=True,
+                      max_slots=batch + 1, dtype="float32")
+    own, lib, touched = count_step_kernels(rt, batch, context)
+    dec = time_decode(rt, batch, context, steps=6, warmup=3)
+    step_bytes = 2 * decode_step_bytes(cfg, batch, context, touched)
+    pms = time_prefill(rt, 2048, reps=3, warmup=1)
+    prop = torch.cuda.get_device_properties(0)
+    mhz = float(getattr(prop, "clock_rate", 1965000)) / 1e3      # the maximum SM clock
+    peak = prop.multi_processor_count * FP32_FMA_PER_SM_PER_CLOCK * 2 * mhz * 1e6
+    fl = prefill_flops(cfg, 2048)
+    out = {
+        f"fp32_decode_b{batch}": round(dec["tok_s"], 1),
+        f"fp32_decode_b{batch}_ms": round(dec["ms_per_step"], 3),
+        f"fp32_decode_b{batch}_hbm_frac": round(step_bytes / (dec["ms_per_step"] / 1e3) / 1e9
+                                                / hbm_peak, 4),
+        "fp32_prefill_2048": round(2048 / (pms / 1e3), 1),
+        "fp32_prefill_2048_ms": round(pms, 2),
+        "fp32_prefill_2048_ffma_frac": round(fl / (pms / 1e3) / peak, 4),
+        "fp32_ffma_peak_tflops": round(peak / 1e12, 1),
+        "fp32_library_gemms": lib,
+    }
+    del rt
+    torch.cuda.empty_cache()
+    return out
+
+
 def breakdown(rt, batch, context, steps, prefill_tokens=0):
     """Device time per kernel face over eager steps (CUDA events around every call of
     the kernel module), as a table sorted by share.  A diagnostic, not a bench value."""
@@ -481,9 +517,82 @@ def serving(args):
         "steps": st["steps"], "graph_replays": st["graph_replays"],
         "preemptions": st["preemptions"],
         "tokens_prefilled_incl_recompute": st["tokens_prefilled"],
+        "host_seconds": st["host_seconds"], "graph_captures": st["graph_captures"],
+        "capture_seconds": st["capture_seconds"], "eager_steps": st["eager_steps"],
+        "host_share_not_waiting": round(1.0 - st["host_seconds"]["wait"] / dt, 3),
         "pool_pages": pages, "pool_fraction_of_demand": args.pool_fraction,
         "finish_reasons": reasons, "layers": layers, "layers_of_config": FULL_LAYERS}))
     return 0
+
+
+def serving_check(args):
+    """The correctness claim of the serving workload: preemption by recompute does not
+    change what a request generates.  The same requests run greedily in 32-bit twice,
+    with a roomy cache pool and with one sized to a fraction of the demand (so that
+    sequences are preempted and recomputed), at the serving configuration's layer sizes
+    with few layers and smaller counts.  Two runs batch tokens differently, which moves
+    32-bit sums by rounding; so where a request's tokens differ, the logits at the first
+    difference are computed once more for that request alone, and the two tokens chosen
+    must be level there within the 32-bit bound (2e-5 of the largest logit)."""
+    import torch
+    from inferx_b200 import Engine, EngineConfig, Request, SamplingParams
+    from inferx_b200.engine import StepEntry
+    layers = args.layers
+    cfg = dict(A27B, num_hidden_layers=layers, decoder_sparse_step=2, norm_topk_prob=True,
+               use_sliding_window=True, sliding_window=4096, max_window_layers=max(0, layers - 1),
+               torch_dtype="float32")
+    n_req, max_prompt, new_tokens = args.requests, args.max_prompt, args.new_tokens
+    g = torch.Generator().manual_seed(5)
+    lens = torch.randint(16, max_prompt + 1, (n_req,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    page = 16
+    demand = sum(-(-(n + new_tokens) // page) for n in sorted(lens)[-args.max_num_seqs:])
+    longest = -(-(max_prompt + new_tokens) // page) + 1
+
+    def run(pages):
+        eng = Engine.create(EngineConfig(
+            config_json=cfg, dtype="float32", max_num_seqs=args.max_num_seqs,
+            max_model_len=max_prompt + new_tokens + 8, max_num_batched_tokens=2048,
+            prefill_chunk=512, block_size=page, num_gpu_blocks_override=pages))
+        outs = eng.generate([Request(p, SamplingParams(max_tokens=new_tokens, ignore_eos=True))
+                             for p in prompts])
+        return eng, [c.output_tokens for c in outs], eng.stats()["preemptions"]
+
+    tight_pages = max(longest, int(args.pool_fraction * demand))
+    eng, tight, pre_tight = run(tight_pages)
+    del eng
+    torch.cuda.empty_cache()
+    eng, roomy, pre_roomy = run(demand + longest)
+    identical = level = 0
+    worst_gap = 0.0
+    failures = []
+    rt = eng.runtime
+    for i, (a, b) in enumerate(zip(roomy, tight)):
+        if a == b:
+            identical += 1
+            continue
+        j = next(k for k in range(min(len(a), len(b))) if a[k] != b[k])
+        seq = prompts[i] + a[:j]
+        rt.manager.open(("check", i))
+        assert rt.manager.reserve(("check", i), len(seq))
+        row = rt.executor.step([StepEntry(("check", i), seq, [len(seq) - 1])])[0].float()
+        gap = abs(float(row[a[j]] - row[b[j]])) / float(row.abs().max())
+        top = float(row.max() - max(row[a[j]], row[b[j]])) / float(row.abs().max())
+        rt.manager.close(("check", i))
+        worst_gap = max(worst_gap, gap, top)
+        if gap <= 2e-5 and top <= 2e-5:
+            level += 1
+        else:
+            failures.append({"request": i, "position": j, "gap": gap, "below_top": top})
+    ok = not failures and pre_tight >= 1 and pre_roomy == 0
+    print(json.dumps({
+        "workload": "serving --check", "dtype": "float32", "layers": layers,
+        "requests": n_req, "max_num_seqs": args.max_num_seqs, "new_tokens": new_tokens,
+        "preemptions_tight": pre_tight, "preemptions_roomy": pre_roomy,
+        "pool_pages_tight": tight_pages, "identical_requests": identical,
+        "level_at_first_difference": level, "worst_relative_gap": worst_gap,
+        "failures": failures, "ok": ok}))
+    return 0 if ok else 1
 
 
 def reference_arm():
@@ -509,11 +618,14 @@ def main(argv=None):
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--serving", action="store_true",
                     help="continuous batching with preemption instead of the bench line")
-    ap.add_argument("--requests", type=int, default=64)
-    ap.add_argument("--max-num-seqs", type=int, default=16)
-    ap.add_argument("--max-prompt", type=int, default=6000)
-    ap.add_argument("--new-tokens", type=int, default=256)
-    ap.add_argument("--pool-fraction", type=float, default=0.6)
+    ap.add_argument("--check", action="store_true",
+                    help="with --serving: preempted and unpreempted runs generate the same "
+                         "(32-bit, greedy, few layers)")
+    ap.add_argument("--requests", type=int, default=None, help="64; with --check 24")
+    ap.add_argument("--max-num-seqs", type=int, default=None, help="16; with --check 8")
+    ap.add_argument("--max-prompt", type=int, default=None, help="6000; with --check 1500")
+    ap.add_argument("--new-tokens", type=int, default=None, help="256; with --check 48")
+    ap.add_argument("--pool-fraction", type=float, default=None, help="0.6; with --check 0.3")
     ap.add_argument("--breakdown", choices=["decode", "prefill"],
                     help="print device time per kernel face instead of the bench line")
     args = ap.parse_args(argv)
@@ -533,6 +645,15 @@ def main(argv=None):
         args.layers = full_layers
     if args.context is None:
         args.context = sizes["context"]
+    small = bool(args.check)
+    for key, full, few in (("requests", 64, 24), ("max_num_seqs", 16, 8), ("max_prompt", 6000, 1500),
+                           ("new_tokens", 256, 48), ("pool_fraction", 0.6, 0.3)):
+        if getattr(args, key) is None:
+            setattr(args, key, few if small else full)
+    if args.serving and args.check:
+        if "--layers" not in (argv or sys.argv):
+            args.layers = 3
+        return serving_check(args)
     if args.serving:
         return serving(args)
     hbm_peak, tf_peak, peak_src = peaks()
@@ -615,6 +736,20 @@ def main(argv=None):
                           "ms": round(pms, 3),
                           "frac": round(fl / (pms / 1e3) / (tf_peak * 1e12), 4),
                           "flops": int(fl), "peak_tflops": tf_peak, "peak_source": peak_src}
+        # further contexts and prompt lengths (what the cache pool of the widest run holds)
+        for c in (16384, 32768):
+            if B * (c + extra + 16) <= pool_tokens:
+                d = time_decode(rt, B, c, max(8, args.steps // 4), args.warmup)
+                by = decode_step_bytes(cfg, B, c, touched)
+                points[f"decode_b{B}_ctx{c}_ms"] = round(d["ms_per_step"], 4)
+                points[f"decode_b{B}_ctx{c}_hbm_frac"] = round(
+                    by / (d["ms_per_step"] / 1e3) / 1e9 / hbm_peak, 4)
+        for t in (4096, 8192):
+            if t + 64 <= pool_tokens:
+                ms = time_prefill(rt, t, reps=3, warmup=2)
+                points[f"prefill_{t}_tok_s"] = round(t / (ms / 1e3), 1)
+                points[f"prefill_{t}_frac"] = round(
+                    prefill_flops(cfg, t) / (ms / 1e3) / (tf_peak * 1e12), 4)
         out["points"] = points
     del rt
     torch.cuda.empty_cache()
@@ -623,6 +758,8 @@ def main(argv=None):
     elif not args.skip_points:
         out["e2e"] = {"unmeasured": "a second copy of the weights for the entry point's own "
                                     "engine is not made at these sizes"}
+    if not args.skip_points and args.sizes == "a2.7b":
+        out["points"].update(fp32_points(cfg, B, C, hbm_peak))
     print(json.dumps(out))
     return 0
 

@@ -12,6 +12,7 @@ less than one sequence of ``max_model_len``.
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Any, Dict, Hashable, Iterator, List, Mapping, Optional, Sequence
 
@@ -119,6 +120,10 @@ class Engine:
         self._next_id = 0
         self.tokens_generated = 0
         self.tokens_prefilled = 0
+        # wall-clock seconds of the host's part of every step, by what it was spent on
+        # (the reference reports the same split, docs/ARCHITECTURE.md:172-180): planning,
+        # building and launching the step, waiting for the sampled ids, committing
+        self.seconds = {"plan": 0.0, "launch": 0.0, "wait": 0.0, "commit": 0.0}
 
     # ------------------------------------------------------------------
     @classmethod
@@ -167,17 +172,29 @@ class Engine:
 
     def step(self) -> List[TokenDelta]:
         """One scheduler step; the tokens it produced."""
+        clock = time.perf_counter
+        t0 = clock()
         planned = self.scheduler.prepare_step()
         if not planned:
             return []
         entries = [StepEntry(e.id, e.tokens, [len(e.tokens) - 1] if e.sample else [])
                    for e in planned]
+        t1 = clock()
         logits = self.runtime.executor.step(entries)
         sampled: List[int] = []
         rows = [e for e in planned if e.sample]
-        if rows:
-            sampled = self.sampler(logits, rows).tolist()
+        ids = self.sampler(logits, rows) if rows else None
+        t2 = clock()
+        if ids is not None:
+            sampled = ids.tolist()          # the one wait of the step
+        t3 = clock()
         deltas = self.scheduler.commit_step(sampled)
+        t4 = clock()
+        sec = self.seconds
+        sec["plan"] += t1 - t0
+        sec["launch"] += t2 - t1
+        sec["wait"] += t3 - t2
+        sec["commit"] += t4 - t3
         self.tokens_generated += len(sampled)
         self.tokens_prefilled += sum(len(e.tokens) for e in planned) - len(rows)
         return deltas
@@ -209,9 +226,13 @@ class Engine:
             "tokens_generated": self.tokens_generated,
             "tokens_prefilled": self.tokens_prefilled,
             "graph_replays": self.runtime.executor.graph_replays,
+            "graph_captures": self.runtime.executor.graph_captures,
+            "capture_seconds": round(self.runtime.executor.capture_seconds, 4),
+            "eager_steps": self.runtime.executor.eager_steps,
             "running": len(self.scheduler.running),
             "waiting": len(self.scheduler.waiting),
             "pages_free": [p.free_count for p in mgr.pools],
             "pages_total": [p.num_pages for p in mgr.pools],
             "cache_bytes": self.runtime.storage.bytes(),
+            "host_seconds": {k: round(v, 4) for k, v in self.seconds.items()},
         }

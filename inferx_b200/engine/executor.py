@@ -24,6 +24,7 @@ advances the request's length after the step.
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
@@ -162,6 +163,11 @@ class Executor:
         self._graphs = GraphCache()
         self._graph_pool = None
         self.graph_replays = 0
+        self.graph_captures = 0
+        self.eager_steps = 0
+        self.capture_seconds = 0.0        # host time spent recording steps
+        self._staging: List[list] = []
+        self._staging_turn = -1
         self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------------
@@ -319,14 +325,39 @@ class Executor:
             cu_q_prompt=seg(_CU_Q_PROMPT))
         return ctx, (seg(_LOGIT_ROWS) if lay.R else None)
 
+    # Index arrays of steps that are not replayed travel through a small ring of pinned
+    # staging buffers that are kept: page-locking host memory costs far more than a step's
+    # copy, so it is not done per step.  A buffer is reused once the copy that last read it
+    # has completed (an event recorded behind that copy).
+    STAGING_BUFFERS = 4
+
+    def _upload(self, lay: _Layout) -> torch.Tensor:
+        """The step's index arrays on the device (one asynchronous copy)."""
+        if self.device.type != "cuda":
+            host = torch.zeros(lay.total, dtype=torch.int32)
+            self._fill(host, lay)
+            return host
+        ring = self._staging
+        i = self._staging_turn = (self._staging_turn + 1) % self.STAGING_BUFFERS
+        if len(ring) <= i:
+            ring.append([None, None])
+        buf, ev = ring[i]
+        if ev is not None:
+            ev.synchronize()
+        if buf is None or buf.numel() < lay.total:
+            buf = torch.zeros(max(lay.total, 4096), dtype=torch.int32).pin_memory()
+        self._fill(buf, lay)
+        dev = torch.empty(lay.total, dtype=torch.int32, device=self.device)
+        dev.copy_(buf[:lay.total], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        ring[i] = [buf, ev]
+        return dev
+
     def build_context(self, entries: Sequence[StepEntry]):
         """(StepContext, logit_rows tensor or None, number of wanted rows) for an eager step."""
         lay = self._layout(entries, bucket_tables=False)
-        host = torch.zeros(lay.total, dtype=torch.int32)
-        self._fill(host, lay)
-        if self.device.type == "cuda":
-            host = host.pin_memory()
-        dev = host.to(self.device, non_blocking=True)
+        dev = self._upload(lay)
         self.last_h2d_bytes = lay.total * 4
         ctx, rows = self._context(dev, lay, static=False)
         return ctx, rows, lay.R
@@ -342,13 +373,13 @@ class Executor:
             # set and the library's plans made outside of any capture.  It is built like
             # a recorded step (bucketed tables, no per-step host values), so that a part
             # which cannot be recorded fails here, at the first step, and not later.
-            host = torch.zeros(lay.total, dtype=torch.int32).pin_memory()
-            self._fill(host, lay)
-            dev = host.to(self.device, non_blocking=True)
+            dev = self._upload(lay)
             self.last_h2d_bytes = lay.total * 4
             ctx, rows = self._context(dev, lay, static=True)
+            self.eager_steps += 1
             return self.model.forward(ctx, self.caches, rows)
         if slot is None:
+            t_capture = time.perf_counter()
             host = torch.zeros(lay.total, dtype=torch.int32).pin_memory()
             dev = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
             self._fill(host, lay)
@@ -368,6 +399,8 @@ class Executor:
             slot = _Graph(graph, dev, [host, torch.zeros_like(host).pin_memory()], [None, None],
                           logits)
             self._graphs.put(key, slot, decode)
+            self.graph_captures += 1
+            self.capture_seconds += time.perf_counter() - t_capture
         else:
             i = slot.turn = 1 - slot.turn
             if slot.copied[i] is not None:
@@ -397,6 +430,7 @@ class Executor:
         if self.use_graphs:
             return self._graph_step(entries)
         ctx, rows, _ = self.build_context(entries)
+        self.eager_steps += 1
         return self.model.forward(ctx, self.caches, rows)
 
     # Kernels with bounded waits record a wait that ran out in a status word on the
