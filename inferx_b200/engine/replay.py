@@ -77,9 +77,24 @@ class ReplaySession:
         return logits
 
 
-def run_stream(session: ReplaySession, lines: Iterable[str], out_dir: str, report=None) -> int:
+def wanted_rows(session: ReplaySession, step: Mapping[str, Any]):
+    """[(request id, position)] of the rows a step's logits file will hold, in order: what
+    the reference's logits files carry beside the values (scripts/gen_reference_logits.py:
+    15-23).  Call before the step runs."""
+    out = []
+    for e in step.get("entries", []):
+        if not e.get("tokens"):
+            continue
+        base = session.manager.length(e["id"]) if session.manager.has(e["id"]) else 0
+        out += [(e["id"], base + int(w)) for w in e.get("want", [])]
+    return out
+
+
+def run_stream(session: ReplaySession, lines: Iterable[str], out_dir: str, report=None,
+               index: bool = False) -> int:
     """Replay JSON lines; write ``<out_dir>/<step>.f32`` for steps that want logits
-    and call ``report(step)`` after every step."""
+    and call ``report(step)`` after every step.  With ``index``, a step that wants
+    logits also gets ``<step>.rows.json``: the request id and position of every row."""
     os.makedirs(out_dir, exist_ok=True)
     n = 0
     for line in lines:
@@ -87,10 +102,15 @@ def run_stream(session: ReplaySession, lines: Iterable[str], out_dir: str, repor
         if not line:
             continue
         step = json.loads(line)
+        tags = wanted_rows(session, step) if index else None
         logits = session.run_step(step)
         if logits is not None:
             arr = logits.detach().to("cpu", torch.float32).contiguous().numpy()
             arr.astype("<f4").tofile(os.path.join(out_dir, f"{step['step']}.f32"))
+            if index:
+                with open(os.path.join(out_dir, f"{step['step']}.rows.json"), "w") as f:
+                    json.dump({"vocab": int(arr.shape[1]),
+                               "rows": [{"id": r, "position": p} for r, p in tags]}, f)
         elif session.executor.device.type == "cuda":
             torch.cuda.synchronize()
         session.executor.poll_errors()
@@ -113,6 +133,8 @@ def main(argv=None) -> int:
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     ap.add_argument("--max-live", type=int, default=8, help="requests alive at once")
+    ap.add_argument("--index", action="store_true",
+                    help="also write <step>.rows.json: request id and position of each row")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("trace_run: no CUDA device; this engine has no CPU path", file=sys.stderr)
@@ -125,5 +147,5 @@ def main(argv=None) -> int:
         sys.stdout.flush()
 
     # one line at a time: the sender may wait for "done <step>" before it writes the next
-    run_stream(session, iter(sys.stdin.readline, ""), args.out, report)
+    run_stream(session, iter(sys.stdin.readline, ""), args.out, report, index=args.index)
     return 0

@@ -38,3 +38,27 @@ def test_pool_too_small_is_reported(tmp_path):
     sess = ReplaySession(d, "float32", 64, page_size=16, device="cpu", ops=host_ops)
     with pytest.raises(ReplayError, match="no page left"):
         mc.run_trace(sess, traces.whole(reqs))
+
+
+def test_replayed_rows_are_tagged_with_request_and_position(tmp_path):
+    import json
+    from inferx_b200.engine.replay import run_stream
+    d = mc.make_model_dir(TINY_A, tmp_path / "m", 0)
+    reqs = mc.make_requests(TINY_A, [9, 4], 0)
+    steps = traces.mixed(reqs, max_live=2, seed=1, decode_tail=3)
+    sess = ReplaySession(d, "float32", traces.peak_tokens(steps), page_size=4, device="cpu",
+                         ops=host_ops)
+    out = tmp_path / "out"
+    run_stream(sess, [json.dumps(s) for s in steps], str(out), index=True)
+    pos = {}
+    for st in steps:
+        want = [(e["id"], pos.get(e["id"], 0) + w) for e in st["entries"] for w in e["want"]]
+        for e in st["entries"]:
+            pos[e["id"]] = pos.get(e["id"], 0) + len(e["tokens"])
+        path = out / f"{st['step']}.rows.json"
+        if not want:
+            assert not path.exists()
+            continue
+        tagged = json.loads(path.read_text())
+        assert tagged["vocab"] == TINY_A["vocab_size"]
+        assert [(r["id"], r["position"]) for r in tagged["rows"]] == want
