@@ -474,6 +474,73 @@ def breakdown(rt, batch, context, steps, prefill_tokens=0):
     return "\n".join(lines)
 
 
+def marginal(rt, batch, context, steps):
+    """What each kernel face costs *inside* the recorded step: the decode step is timed
+    again with that face's launches left out (it hands back the result of its first
+    call), and the difference is what the face adds to the step where it runs, with
+    dependent launch, the side stream and its neighbours as they are.  A diagnostic, not a
+    bench value: the steps it times compute nonsense."""
+    import torch
+    from inferx_b200.engine.executor import GraphCache
+    from inferx_b200.kernels import ops
+
+    def run():
+        rt.executor._graphs = GraphCache()       # the same shape must be recorded anew
+        return time_decode(rt, batch, context, steps, 4)["ms_per_step"]
+
+    # with a face left out, the expert offsets are no longer two launches back
+    settled = ops.grouped_down
+    ops.grouped_down = lambda act, offsets, w, offsets_settled=False: settled(act, offsets, w)
+    layers = rt.model.spec.schedule.__len__()
+    base = run()
+    lines = [f"decode step, batch {batch}, context {context}: {base:.4f} ms",
+             f"{'left out':44s} {'ms/step':>9s} {'us/layer':>9s} {'us/step':>9s}"]
+
+    def without(names, pred=None):
+        cache, orig = {}, {n: getattr(ops, n) for n in names}
+
+        def fake(n, fn):
+            def call(*a, **k):
+                if pred is not None and not pred(n, a):
+                    return fn(*a, **k)
+                key = (n,) + tuple(tuple(x.shape) for x in a if isinstance(x, torch.Tensor))
+                if key not in cache:
+                    cache[key] = fn(*a, **k)
+                return cache[key]
+            return call
+        for n, fn in orig.items():
+            setattr(ops, n, fake(n, fn))
+        try:
+            return run()
+        finally:
+            for n, fn in orig.items():
+                setattr(ops, n, fn)
+
+    hidden = rt.model.spec.hidden
+    faces = [
+        ("attention over the cache (+ merge)", ["paged_attention"], None),
+        ("QKV product + rotation + cache write", ["qkv_project_rope_append"], None),
+        ("output projection", ["linear"], lambda n, a: tuple(a[1].shape) == (hidden, hidden)),
+        ("vocabulary projection", ["linear"], lambda n, a: a[1].shape[0] == rt.vocab_size),
+        ("routed gate/up + SwiGLU", ["grouped_gate_up_swiglu"], None),
+        ("routed down", ["grouped_down"], None),
+        ("shared expert (side stream)", ["gate_up_swiglu", "linear"],
+         lambda n, a: n == "gate_up_swiglu" or a[1].shape[0] == hidden and a[1].shape[1] != hidden),
+        ("router logits + selection", ["router_topk"], None),
+        ("dispatch tables", ["moe_dispatch"], None),
+        ("both norms (+ combine)", ["add_rmsnorm"], None),
+        ("sampling", ["sample"], None),
+    ]
+    try:
+        for name, names, pred in faces:
+            t = without(names, pred)
+            lines.append(f"{name:44s} {t:9.4f} {(base - t) * 1e3 / layers:9.1f} "
+                         f"{(base - t) * 1e3:9.0f}")
+    finally:
+        ops.grouped_down = settled
+    return "\n".join(lines)
+
+
 def serving(args):
     """Continuous batching under memory pressure, in the shape of BASELINE.json's fifth
     configuration: A2.7B layer sizes with every second layer dense, renormalised top-k
@@ -628,6 +695,8 @@ def main(argv=None):
     ap.add_argument("--pool-fraction", type=float, default=None, help="0.6; with --check 0.3")
     ap.add_argument("--breakdown", choices=["decode", "prefill"],
                     help="print device time per kernel face instead of the bench line")
+    ap.add_argument("--marginal", action="store_true",
+                    help="print what each kernel face adds to the recorded decode step")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm()
@@ -661,7 +730,7 @@ def main(argv=None):
     B, C = args.batch, args.context
     big_b, big_c = sizes["big_batch"], C
     extra = args.steps + args.warmup + 8
-    points_wanted = not (args.skip_points or args.breakdown)
+    points_wanted = not (args.skip_points or args.breakdown or args.marginal)
     # what the device has to hold: weights, and the cache pool of the widest run (plus
     # the 2,048-token portion of the mixed step); the widest run's context is cut, in
     # steps of 4096, until it fits
@@ -682,6 +751,9 @@ def main(argv=None):
     rt = make_runtime(cfg, 1, pool_tokens, 0, use_graphs=not args.no_graphs,
                       max_slots=max(B, big_b if points_wanted else B) + 1)
 
+    if args.marginal:
+        print(marginal(rt, B, C, min(args.steps, 24)))
+        return 0
     if args.breakdown:
         print(breakdown(rt, B, C, min(args.steps, 4),
                         prefill_tokens=2048 if args.breakdown == "prefill" else 0))

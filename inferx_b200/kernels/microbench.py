@@ -6,6 +6,7 @@
     python -m inferx_b200.kernels.microbench attn_prefill --tokens 2048 [--form tc|mma]
     python -m inferx_b200.kernels.microbench attn_prefill --tokens 512 --context 8192 [--splits N]
     python -m inferx_b200.kernels.microbench router --tokens 2048
+    python -m inferx_b200.kernels.microbench qkv --rows 8 [--separate]
     python -m inferx_b200.kernels.microbench grouped --tokens 2048
 
 Each case runs one kernel face at Qwen1.5-MoE-A2.7B sizes (or the sizes given),
@@ -142,6 +143,36 @@ def dense(args):
             "TFLOPs": round(2 * M * N * K / us / 1e6, 2)}
 
 
+def qkv(args):
+    """The QKV projection of a few-token step with bias, rotation and cache write: the one
+    fused kernel, or (--separate) the product followed by the rotation kernel."""
+    from . import ops
+    T, H, heads, kvh, hd, page = args.rows, args.hidden, args.heads, args.kv_heads, args.head_dim, args.page
+    dt = torch.bfloat16
+    width = (heads + 2 * kvh) * hd
+    n = _copies(width * H * 2)
+    ws = [torch.randn(width, H, device="cuda", dtype=dt) * 0.02 for _ in range(n)]
+    bias = torch.randn(width, device="cuda") * 0.1
+    x = torch.randn(T, H, device="cuda", dtype=dt)
+    positions = torch.arange(4000, 4000 + T, dtype=torch.int32, device="cuda")
+    inv = (10000.0 ** (-2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float().cuda()
+    kc = torch.zeros(T + 1, kvh, page, hd, device="cuda", dtype=dt)
+    vc = torch.zeros_like(kc)
+    slots = (torch.arange(T, dtype=torch.int32, device="cuda") * page)
+    ops.set_dependent_launch(True)
+
+    def fused(i):
+        ops.qkv_project_rope_append(x, ws[i], bias, positions, inv, hd, heads, kvh, hd, kc, vc, slots)
+
+    def separate(i):
+        ops.qkv_rope_append(ops.linear(x, ws[i]), bias, positions, inv, hd, heads, kvh, hd, kc, vc,
+                            slots)
+    us = _time(separate if args.separate else fused, n, args.iters)
+    nbytes = width * H * 2
+    return {"case": "qkv", "rows": T, "width": width, "k": H, "fused": not args.separate,
+            "us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1)}
+
+
 def router(args):
     from . import ops
     T, H, E, k = args.tokens, args.hidden, args.experts, args.top_k
@@ -192,7 +223,8 @@ def attn_prefill(args):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("case", choices=["attn_decode", "grouped", "dense", "attn_prefill", "router"])
+    ap.add_argument("case", choices=["attn_decode", "grouped", "dense", "attn_prefill", "router",
+                                     "qkv"])
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
@@ -212,6 +244,8 @@ def main(argv=None):
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--separate", action="store_true",
+                    help="qkv: the product and the rotation as two kernels")
     ap.add_argument("--eager", action="store_true", help="plain launches, no graph capture")
     args = ap.parse_args(argv)
     args.context_given = any(a == "--context" or a.startswith("--context=") for a in (argv or sys.argv[1:]))
