@@ -82,7 +82,8 @@ struct TcItem {
 // prefix of tiles per expert), feature tile w % f_tiles.
 template <int BT>
 __device__ __forceinline__ TcItem tc_item(int w, int f_tiles, const int* tile_start,
-                                          const int* __restrict__ offsets, int E) {
+                                          const int* __restrict__ offsets, int E,
+                                          int f_item = TC_BF) {
   const int tt = w / f_tiles;
   int lo = 0, hi = E;                       // largest e with tile_start[e] <= tt
   while (hi - lo > 1) {
@@ -96,17 +97,22 @@ __device__ __forceinline__ TcItem tc_item(int w, int f_tiles, const int* tile_st
   const int per = tc_tile_rows(rows, tiles_e);
   it.m0 = r0 + (tt - tile_start[lo]) * per;
   it.n_valid = max(0, min(r0 + rows - it.m0, per));
-  it.f0 = (w - tt * f_tiles) * TC_BF;
+  it.f0 = (w - tt * f_tiles) * f_item;
   return it;
 }
 
 // ---------------------------------------------------------------------------
-template <bool DUAL, int BT>
+// MODE 0: one weight tile an item; 1: gate and up tiles, SwiGLU epilogue; 2: two
+// neighbouring feature tiles, both stored.
+template <int MODE, int BT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_w,
                        const int* __restrict__ offsets, bf16* __restrict__ out, int N, int K,
                        int E, int w_rows_per_expert, int* __restrict__ status) {
+  constexpr bool DUAL = MODE != 0;      // two weight tiles and two accumulators an item
+  constexpr bool SWIGLU = MODE == 1;
+  constexpr int F_ITEM = MODE == 2 ? 2 * TC_BF : TC_BF;   // output features of an item
   constexpr int A_BYTES = BT * TC_BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + TC_W_BYTES * (DUAL ? 2 : 1);
   constexpr int STAGES = TC_SMEM_STAGES / STAGE_BYTES;
@@ -131,7 +137,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_tiles = (K + TC_BK - 1) / TC_BK;
-  const int f_tiles = (N + TC_BF - 1) / TC_BF;
+  const int f_tiles = (N + F_ITEM - 1) / F_ITEM;
 
   // prefix of token tiles per expert (warp 2, 32 experts at a time)
   if (warp == 2) {
@@ -182,7 +188,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
       int fill = 0;            // k-tiles issued so far, over all items
       bool ok = true;
       for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
-        const TcItem it = tc_item<BT>(w, f_tiles, tile_start, offsets, E);
+        const TcItem it = tc_item<BT>(w, f_tiles, tile_start, offsets, E, F_ITEM);
         if (it.n_valid <= 0) continue;
         const int boxes = (((it.n_valid + 15) & ~15) + TC_BOX_T - 1) / TC_BOX_T;
         const unsigned stage_tx =
@@ -195,9 +201,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
           mbar_expect_tx(&full_bar[s], stage_tx);
           tma_load_2d(st + A_BYTES, &map_w, kt * TC_BK, it.e * w_rows_per_expert + it.f0,
                       &full_bar[s]);
-          if (DUAL)
+          if (DUAL)   // the up rows of the same features, or the next 128 features
             tma_load_2d(st + A_BYTES + TC_W_BYTES, &map_w, kt * TC_BK,
-                        it.e * w_rows_per_expert + N + it.f0, &full_bar[s]);
+                        it.e * w_rows_per_expert + (SWIGLU ? N : TC_BF) + it.f0, &full_bar[s]);
           for (int b = 0; b < boxes; ++b)
             tma_load_2d(st + b * (TC_BOX_T * TC_BK * 2), &map_a, kt * TC_BK,
                         it.m0 + b * TC_BOX_T, &full_bar[s]);
@@ -215,7 +221,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
       int drain = 0, n_done = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
-        const TcItem it = tc_item<BT>(w, f_tiles, tile_start, offsets, E);
+        const TcItem it = tc_item<BT>(w, f_tiles, tile_start, offsets, E, F_ITEM);
         if (it.n_valid <= 0) continue;
         const unsigned idesc = tc_idesc((it.n_valid + 15) & ~15);
         const int buf = n_done % NBUF;
@@ -252,7 +258,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
     const int quarter = warp & 3;              // TMEM lanes this warp may read
     int n_done = 0;
     for (int w = blockIdx.x; w < n_items; w += gridDim.x) {
-      const TcItem it = tc_item<BT>(w, f_tiles, tile_start, offsets, E);
+      const TcItem it = tc_item<BT>(w, f_tiles, tile_start, offsets, E, F_ITEM);
       if (it.n_valid <= 0) continue;
       const int buf = n_done % NBUF;
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (n_done / NBUF) & 1, abortp))) {
@@ -282,7 +288,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float a = g[i];
-          if (DUAL) a = __fdividef(a, 1.0f + __expf(-a)) * u[i];
+          if (SWIGLU) a = __fdividef(a, 1.0f + __expf(-a)) * u[i];
           r[i] = __float2bfloat16_rn(a);
         }
         // a warp's 32 threads hold 32 neighbouring features of one token: 64-byte stores
@@ -291,6 +297,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int i = 0; i < 32; ++i)
           if (i < n_here) dst[(size_t)i * N] = r[i];
+        if (MODE == 2) {        // the second tile's features, 128 further on
+          const int n_second = f + TC_BF < N ? it.n_valid - c0 : 0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < n_second) dst[(size_t)i * N + TC_BF] = __float2bfloat16_rn(u[i]);
+        }
       }
       ++n_done;
     }
@@ -329,7 +341,7 @@ IX_API int ix_gather_rows(const void* src, const int* rows, void* dst, int n_row
 // a: [A_rows, K] bf16 grouped rows; w: [E, (dual ? 2N : N), K] bf16; out: [A_rows, N] bf16.
 // status: one int in device memory, zero before the first call; a bounded wait that
 // ran out leaves a nonzero code there.
-template <bool DUAL, int BT>
+template <int MODE, int BT>
 static int launch_tc(const void* a, const int* offsets, const void* w, void* out, int A_rows,
                      int N, int K, int E, long long w_rows, int* status, cudaStream_t stream) {
   CUtensorMap map_a, map_w;
@@ -346,11 +358,12 @@ static int launch_tc(const void* a, const int* offsets, const void* w, void* out
       sms = 148;
   }
   // every expert can add a partial token tile
+  constexpr int F_ITEM = MODE == 2 ? 2 * TC_BF : TC_BF;
   const long long items =
-      ((long long)tc_tiles_of<BT>(A_rows) + E) * ((N + TC_BF - 1) / TC_BF);
+      ((long long)tc_tiles_of<BT>(A_rows) + E) * ((N + F_ITEM - 1) / F_ITEM);
   const int grid = (int)(items < sms ? items : sms);
   const int smem = TC_SMEM_STAGES + 1024;
-  auto kern = grouped_gemm_tc_kernel<DUAL, BT>;
+  auto kern = grouped_gemm_tc_kernel<MODE, BT>;
   cudaError_t e2 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e2 != cudaSuccess) return (int)e2;
   kern<<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, offsets, (bf16*)out, N, K, E,
@@ -385,7 +398,12 @@ IX_API int ix_grouped_gemm_tc(const void* a, const int* offsets, const void* w, 
     if (bt == 192) return launch_tc<D, 192>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream); \
     return launch_tc<D, 256>(a, offsets, w, out, A_rows, N, K, E, w_rows, status, stream);   \
   } while (0)
-  if (dual) IX_TC(true);
-  IX_TC(false);
+  if (dual) IX_TC(1);
+  // plain: two feature tiles an item when the features fill them (measured at 60 experts
+  // of 2048 x 1408 against one tile an item: 77 us either way at 2,048 tokens, where 480
+  // items on 148 blocks balance worse than 960; 109 against 131 us at 4,096 tokens and
+  // 202 against 241 us at 8,192, where the token tile is read half as often)
+  if (N >= 2 * TC_BF) IX_TC(2);
+  IX_TC(0);
 #undef IX_TC
 }
