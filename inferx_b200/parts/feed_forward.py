@@ -103,14 +103,25 @@ class MoeFeedForward:
 
     # Below this many tokens a step's kernels leave the GPU partly idle; the shared
     # expert (which needs nothing from the router) then runs beside the routed experts,
-    # on a stream of its own.  That pays while the shared expert is small: its products
-    # then cover the router's short kernels and the boundaries between them (69 MB of
-    # shared weights a layer: a decode step of 3.94 against 4.27 ms at batch 8, 13.4
-    # against 13.5 ms at batch 64).  A shared expert whose weights alone keep the memory
-    # busy for tens of microseconds gains nothing from company and gets in the way of
-    # the routed products (440 MB a layer: 19.3 ms beside them, 16.1 ms after them).
+    # on a stream of its own: its products cover the router's short kernels and the
+    # boundaries between them (69 MB of shared weights a layer: a decode step of 3.94
+    # against 4.27 ms at batch 8, 13.4 against 13.5 ms at batch 64).  One case is left
+    # out: a large shared expert in a step of a few tokens, where its products and the
+    # routed ones are the same kind of weight-streaming kernel, each able to keep the
+    # memory busy alone, and beside each other they only take each other's places on the
+    # multiprocessors (440 MB of shared weights a layer at batch 8: 19.3 ms beside, 16.1 ms
+    # after; at batch 1, where the routed products are short, 6.1 beside against 6.6 ms,
+    # and at batch 32, where the routed products are persistent tensor-core kernels, 24.7
+    # against 25.4 ms).
     OVERLAP_MAX_TOKENS = 256
-    OVERLAP_MAX_WEIGHT_BYTES = 160 << 20
+    OVERLAP_LARGE_WEIGHT_BYTES = 160 << 20
+    OVERLAP_LARGE_NOT_FOR_TOKENS = (3, 16)
+
+    def _overlap_shared(self, tokens: int) -> bool:
+        if tokens > self.OVERLAP_MAX_TOKENS:
+            return False
+        lo, hi = self.OVERLAP_LARGE_NOT_FOR_TOKENS
+        return not (self._shared_bytes > self.OVERLAP_LARGE_WEIGHT_BYTES and lo <= tokens <= hi)
 
     def _side_stream(self):
         if self._side is None:
@@ -120,8 +131,7 @@ class MoeFeedForward:
     def forward(self, x, step=None):
         s, ops = self.spec, self.ctx.ops
         shared, side = None, None
-        if self.shared is not None and x.is_cuda and x.shape[0] <= self.OVERLAP_MAX_TOKENS \
-                and self._shared_bytes <= self.OVERLAP_MAX_WEIGHT_BYTES:
+        if self.shared is not None and x.is_cuda and self._overlap_shared(x.shape[0]):
             side = self._side_stream()
             main = torch.cuda.current_stream(x.device)
             side.wait_stream(main)
