@@ -112,7 +112,8 @@ class MoeFeedForward:
     # multiprocessors (440 MB of shared weights a layer at batch 8: 19.3 ms beside, 16.1 ms
     # after; at batch 1, where the routed products are short, 6.1 beside against 6.6 ms,
     # and at batch 32, where the routed products are persistent tensor-core kernels, 24.7
-    # against 25.4 ms).
+    # against 25.4 ms).  Swapping the roles there - the shared expert on the main stream,
+    # the router's short kernels and the dispatch beside it - measured worse still (20.1 ms).
     OVERLAP_MAX_TOKENS = 256
     OVERLAP_LARGE_WEIGHT_BYTES = 160 << 20
     OVERLAP_LARGE_NOT_FOR_TOKENS = (3, 16)
