@@ -402,6 +402,42 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     return out
 
 
+def paged_attention_tiled(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                          block_table: torch.Tensor, cu_q: torch.Tensor, q_pos0: torch.Tensor,
+                          window: int, scale: float):
+    """CUDA-core attention for a ragged batch, tiled (32 queries of a sequence against 64
+    keys at a time in shared memory, fp32 math): sequence s brings the queries
+    q[cu_q[s]:cu_q[s+1]] at positions q_pos0[s], q_pos0[s]+1, ...  Any element type, head
+    sizes that are a multiple of 4 up to 256."""
+    _chk("q", q)
+    _chk("k_cache", k_cache, q.dtype)
+    _chk("v_cache", v_cache, q.dtype)
+    _chk("block_table", block_table, torch.int32)
+    _chk("cu_q", cu_q, torch.int32)
+    _chk("q_pos0", q_pos0, torch.int32)
+    T, heads, hd = q.shape
+    P, kvh, page, chd = k_cache.shape
+    S = q_pos0.numel()
+    if chd != hd or v_cache.shape != k_cache.shape:
+        raise KernelError("paged_attention_tiled: cache geometry differs from the query's")
+    if cu_q.numel() != S + 1 or block_table.shape[0] != S:
+        raise KernelError("paged_attention_tiled: cu_q, q_pos0 and block_table disagree")
+    out = torch.empty_like(q)
+    code = _lib().ix_paged_attention_tiled(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(cu_q), _ptr(q_pos0),
+        _ptr(out), _dtype_code(q), T, S, heads, kvh, hd, page, block_table.shape[1], window,
+        ctypes.c_float(scale), _stream())
+    _check(code, "paged_attention_tiled")
+    _count()
+    return out
+
+
+# A batch with at least this many queries a sequence on average goes to the tiled
+# CUDA-core kernel where the tensor-core kernels do not apply; fewer (single decoded
+# tokens, mostly) to the kernel that gives every (token, head) a block of its own.
+TILED_ATTENTION_MIN_QUERIES = 4
+
+
 # below this many tokens the router runs as two kernels (logits by one warp per (token,
 # expert), then selection); from it on as one fused kernel (equal at 128 tokens, 13 us
 # against 19-21 us at 200-256)
@@ -692,6 +728,11 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             return out
         return paged_attention_prefill(q, k_cache, v_cache, block_table, step.cu_q, step.q_pos0,
                                        window, scale, max_kv_len=step.max_kv_len)
+    if (step.num_tokens >= TILED_ATTENTION_MIN_QUERIES * step.num_seqs
+            and _lib().ix_paged_attention_tiled_applies(hd)
+            and getattr(step, "cu_q", None) is not None):
+        return paged_attention_tiled(q, k_cache, v_cache, block_table, step.cu_q, step.q_pos0,
+                                     window, scale)
     return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,
                                    step.positions, window, scale)
 

@@ -722,3 +722,85 @@ def test_qkv_projection_with_rotation_and_cache_write_in_one_launch(T, K, heads,
     assert same > 0.98, same
     _close(q1.cpu(), q2.cpu(), torch.bfloat16)
     _close(kc1.cpu(), kc2.cpu(), torch.bfloat16)
+
+
+def _close_sum(out, ref, dtype):
+    """For sums of many terms: in 32-bit two orders of summation differ by rounding that
+    grows with the size of the sums, so the bound is 2e-5 of the largest element of the
+    reference (the bound the model tests use for logits); bfloat16 as everywhere."""
+    if dtype == torch.bfloat16:
+        return _close(out, ref, dtype)
+    bound = 2e-5 * float(ref.abs().max())
+    err = float((out.float() - ref.float()).abs().max())
+    assert err <= bound, f"max error {err:.3e} exceeds {bound:.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 37, 50), (9, 130, 64), (16, 256, 2048), (17, 100, 96),
+                                   (70, 64, 33), (300, 193, 260), (129, 129, 1000)])
+def test_cuda_core_product_single_matrix(dtype, M, N, K):
+    """The product of the 32-bit mode for one matrix, plain and with the SwiGLU folded
+    in: the weight-streaming kernel (up to 16 rows) and the tiled kernel, at sizes that
+    are no multiple of a tile, of four (no vector loads) or of anything."""
+    ops = _ops()
+    x, w = _rand((M, K), dtype, seed=M + N), _rand((N, K), dtype, 0.2, seed=K)
+    out = ops.gemm_generic(x.cuda(), w.cuda().unsqueeze(0), None, None, dual=False)
+    _close_sum(out.cpu(), host_ops.linear(x, w).float(), dtype)
+    if N % 2 == 0:
+        act = ops.gemm_generic(x.cuda(), w.cuda().unsqueeze(0), None, None, dual=True)
+        _close_sum(act.cpu(), host_ops.gate_up_swiglu(x, w).float(), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,I,E,k", [(3, 64, 40, 6, 2), (40, 100, 36, 5, 3), (700, 96, 50, 4, 2)])
+def test_cuda_core_product_grouped(dtype, T, H, I, E, k):
+    """The same for experts: a few rows an expert (weights streamed once), dozens (64-row
+    tiles) and hundreds (128-row tiles); empty experts; rows gathered through a list."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(T)
+    idx = torch.stack([torch.randperm(E - 1, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    off, rows, dest = host_ops.moe_dispatch(idx, E)          # the last expert gets no rows
+    x = _rand((T, H), dtype, seed=1)
+    wgu, wd = _rand((E, 2 * I, H), dtype, 0.2, seed=2), _rand((E, H, I), dtype, 0.2, seed=3)
+    act = ops.gemm_generic(x.cuda(), wgu.cuda(), rows.cuda(), off.cuda(), dual=True,
+                           num_out_rows=T * k)
+    ract = host_ops.grouped_gate_up_swiglu(x, rows, off, wgu)
+    _close_sum(act.cpu(), ract.float(), dtype)
+    y = ops.gemm_generic(ract.cuda(), wd.cuda(), None, off.cuda(), dual=False, num_out_rows=T * k)
+    _close_sum(y.cpu(), host_ops.grouped_down(ract, off, wd).float(), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kvh,hd,page,window", [
+    (4, 2, 16, 4, 0), (3, 1, 32, 8, 8), (6, 3, 48, 16, 5), (2, 2, 128, 16, 0), (5, 1, 80, 2, 33),
+    (2, 1, 256, 16, 100), (7, 7, 96, 12, 0), (4, 2, 112, 64, 70)])
+def test_paged_attention_tiled(dtype, heads, kvh, hd, page, window):
+    """The tiled CUDA-core kernel on a ragged batch: whole prompts, a portion that starts
+    deep in its sequence, a two-token portion, a single token; query tiles that end inside
+    a key tile; pages behind the window given back (block table -1, contents poisoned)."""
+    ops = _ops()
+    seq_lens, q_lens = [150, 1, 333, 64, 65, 700, 97], [150, 1, 70, 64, 2, 1, 33]
+    q, kc, vc, bt, seq_of, pos = _paged_case(dtype, heads, kvh, hd, page, window, seq_lens, q_lens,
+                                             seed=hd + window)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    q_pos0 = torch.tensor([n - ql for n, ql in zip(seq_lens, q_lens)], dtype=torch.int32)
+    scale = 1.0 / math.sqrt(hd)
+    ref = host_ops.paged_attention_generic(q, kc, vc, bt, seq_of, pos, window, scale)
+    if window > 0:
+        kc, vc, bt = kc.clone(), vc.clone(), bt.clone()
+        for s, (n, ql) in enumerate(zip(seq_lens, q_lens)):
+            # pages no query of this step can see: wholly before the first query's window
+            for b in range(max(0, n - ql - window + 1) // page):
+                kc[bt[s, b]] = float("nan")
+                vc[bt[s, b]] = float("nan")
+                bt[s, b] = -1
+    out = ops.paged_attention_tiled(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(),
+                                    torch.tensor(cu, dtype=torch.int32).cuda(), q_pos0.cuda(),
+                                    window, scale)
+    assert torch.isfinite(out).all()
+    if dtype == torch.float32:
+        torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-5)
+    else:
+        _close(out.cpu(), ref, dtype)
