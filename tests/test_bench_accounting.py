@@ -34,7 +34,7 @@ def test_decode_step_bytes_are_weights_used_once_plus_the_live_cache():
     kv = batch * context * 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2 * cfg["num_hidden_layers"]
     want = wb["layers"] * (wb["per_layer_fixed"] + touched * wb["per_expert"]) + wb["head"] + kv
     assert abs(got - want) <= 1e-4 * want
-    assert 19.5e9 < got < 20.5e9          # the survey's figure for this point: about 20.1 GB
+    assert 19.5e9 < got < 20.5e9          # worked out by hand for this point: about 20.1 GB
 
 
 def test_prefill_flops_of_the_headline_prompt():
