@@ -126,7 +126,7 @@ def grouped(args):
 def dense(args):
     from . import ops
     M, N, K = args.rows, args.n, args.k
-    dt = torch.bfloat16
+    dt = torch.float32 if args.dtype == "float32" else torch.bfloat16
     n = _copies(N * K * 2)
     ws = [torch.randn(N, K, device="cuda", dtype=dt) * 0.02 for _ in range(n)]
     x = torch.randn(M, K, device="cuda", dtype=dt)
@@ -137,8 +137,9 @@ def dense(args):
         else:
             ops.linear(x, ws[i])
     us = _time(fn, n, args.iters)
-    nbytes = N * K * 2
+    nbytes = N * K * (4 if dt == torch.float32 else 2)
     return {"case": "dense", "rows": M, "n": N, "k": K, "swiglu": bool(args.swiglu),
+            "dtype": args.dtype,
             "us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1),
             "TFLOPs": round(2 * M * N * K / us / 1e6, 2)}
 
@@ -194,7 +195,7 @@ def router(args):
 def attn_prefill(args):
     from . import ops
     T, heads, kvh, hd, page = args.tokens, args.heads, args.kv_heads, args.head_dim, args.page
-    dt = torch.bfloat16
+    dt = torch.float32 if args.dtype == "float32" else torch.bfloat16
     C = max(args.context if args.context_given else T, T)   # keys: the portion ends the context
     pages = -(-C // page)
     kc = torch.randn(pages, kvh, page, hd, device="cuda", dtype=dt)
@@ -211,8 +212,11 @@ def attn_prefill(args):
     scale = 1.0 / math.sqrt(hd)
 
     def fn(i):
-        ops.paged_attention_prefill(q, kc, vc, bt, step.cu_q, step.q_pos0, args.window, scale,
-                                    kernel=args.form or None, splits=args.splits or None)
+        if args.form == "tiled":      # the CUDA-core kernel (any element type)
+            ops.paged_attention_tiled(q, kc, vc, bt, step.cu_q, step.q_pos0, args.window, scale)
+        else:
+            ops.paged_attention_prefill(q, kc, vc, bt, step.cu_q, step.q_pos0, args.window, scale,
+                                        kernel=args.form or None, splits=args.splits or None)
     us = _time(fn, 1, args.iters)
     flops = 4 * heads * hd * (T * T / 2 + T * (C - T))
     return {"case": "attn_prefill", "tokens": T, "context": C, "heads": heads, "head_dim": hd,
@@ -235,7 +239,7 @@ def main(argv=None):
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--splits", type=int, default=0)
-    ap.add_argument("--form", default="", help="attn_decode: tma, mma or scalar; attn_prefill: tc or mma (default: auto)")
+    ap.add_argument("--form", default="", help="attn_decode: tma, mma or scalar; attn_prefill: tc, mma or tiled (default: auto)")
     ap.add_argument("--hidden", type=int, default=2048)
     ap.add_argument("--inter", type=int, default=1408)
     ap.add_argument("--experts", type=int, default=60)
@@ -244,6 +248,8 @@ def main(argv=None):
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="dense, attn_prefill --form tiled: the element type")
     ap.add_argument("--separate", action="store_true",
                     help="qkv: the product and the rotation as two kernels")
     ap.add_argument("--eager", action="store_true", help="plain launches, no graph capture")
