@@ -62,3 +62,31 @@ def test_replayed_rows_are_tagged_with_request_and_position(tmp_path):
         tagged = json.loads(path.read_text())
         assert tagged["vocab"] == TINY_A["vocab_size"]
         assert [(r["id"], r["position"]) for r in tagged["rows"]] == want
+
+
+def test_host_mirrors_of_a_step_are_shape_or_value(tmp_path):
+    """What a part may read on the host: the step's shape always; the step's values
+    (lengths, state slots, first live pages) only when the step is not recorded for
+    replay, where they would be baked into the recording."""
+    from inferx_b200.engine.executor import StepEntry
+    d = mc.make_model_dir(TINY_B, tmp_path / "m", 1)
+    sess = ReplaySession(d, "float32", 256, page_size=8, max_live=3, device="cpu", ops=host_ops)
+    mgr, ex = sess.manager, sess.executor
+    for rid, n in (("a", 30), ("b", 5)):
+        mgr.open(rid)
+        assert mgr.reserve(rid, n + 4)
+        mgr.advance(rid, n)            # 'a' is 30 tokens in: its windowed group gave pages back
+    entries = [StepEntry("a", [7], [0]), StepEntry("b", [1, 2, 3], [2])]
+    lay = ex._layout(entries, bucket_tables=False)
+    dev = ex._upload(lay)
+    eager, _ = ex._context(dev, lay, static=False)
+    assert eager.q_lens == [1, 3] and eager.kv_lens == [31, 8] and not eager.captured
+    assert eager.state_slots == [mgr.slot("a"), mgr.slot("b")]
+    assert eager.state_slot.tolist() == eager.state_slots
+    windowed = [g for g in eager.groups if g.window > 0][0]
+    assert windowed.first_live == [mgr.first_live("a", 1), 0] and windowed.first_live[0] >= 2
+    recorded, _ = ex._context(dev, lay, static=True)
+    assert recorded.captured and recorded.q_lens == [1, 3] and recorded.num_decode_seqs == 1
+    assert recorded.kv_lens is None and recorded.state_slots is None
+    assert all(g.first_live is None for g in recorded.groups)
+    assert recorded.kv_len.tolist() == [31, 8]          # the device's copies are always there
