@@ -525,7 +525,7 @@ def test_toy_single_entry_paged_mixer_and_block_arrangement(tmp_path, dtype, gra
 
 
 # ---------------------------------------------------------------------------
-# another position encoding and a feed-forward with routing, defined in the test
+# another position encoding, a feed-forward with routing and another norm, defined in the test
 # ---------------------------------------------------------------------------
 @dataclass(frozen=True)
 class LearnedOffsetSpec:
@@ -585,14 +585,51 @@ class ParityRoutedFeedForward:
         return out
 
 
+@dataclass(frozen=True)
+class CenteredNormSpec:
+    size: int
+    eps: float
+    kind: str = "toy_centered"
+
+
+class CenteredNorm:
+    """A norm that subtracts the mean and has a bias: ``(x - mean) / sqrt(var + eps) * gain
+    + bias``.  Like every norm it first adds the pending contribution into the fp32
+    residual stream, then returns the normalised rows in the run's element type."""
+
+    def __init__(self, spec, ctx, prefix):
+        self.spec, self.ctx, self.prefix = spec, ctx, prefix
+
+    def tensors(self):
+        return [TensorDecl(f"{self.prefix}.weight", (self.spec.size,), keep="float32", init="gain"),
+                TensorDecl(f"{self.prefix}.bias", (self.spec.size,), keep="float32")]
+
+    def bind(self, w):
+        self.gain, self.bias = w[f"{self.prefix}.weight"], w[f"{self.prefix}.bias"]
+
+    def forward(self, resid, delta, rows=None):
+        if delta is not None:
+            resid += delta.float()
+        x = resid if rows is None else resid[rows.long()]
+        c = x - x.mean(-1, keepdim=True)
+        y = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + self.spec.eps) * self.gain + self.bias
+        return y.to(self.ctx.dtype)
+
+
+def _centered(x, gain, bias, eps):
+    c = x - x.mean(-1, keepdim=True)
+    return c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * gain + bias
+
+
 def _toy2_spec(cfg):
     norm = RmsNormSpec(size=cfg.hidden, eps=1e-5)
+    centered = CenteredNormSpec(size=cfg.hidden, eps=1e-3)
     attn = AttentionSpec(hidden=cfg.hidden, heads=3, kv_heads=1, head_dim=16, qkv_bias=True,
                          scale=0.25, window=6,
                          position=LearnedOffsetSpec(head_dim=16, max_positions=64))
-    layers = (LayerSpec("model.layers.0", norm, attn, norm, ParityRoutedSpec(cfg.hidden)),)
+    layers = (LayerSpec("model.layers.0", norm, attn, centered, ParityRoutedSpec(cfg.hidden)),)
     return ModelSpec(architecture="ToyRoutedForCausalLM", vocab_size=cfg.vocab, hidden=cfg.hidden,
-                     layers=layers, schedule=(RunEntry(0),), final_norm=norm, tied_head=False)
+                     layers=layers, schedule=(RunEntry(0),), final_norm=centered, tied_head=False)
 
 
 def _toy2_plain(w, tokens, hidden):
@@ -606,19 +643,21 @@ def _toy2_plain(w, tokens, hidden):
     v = (n @ w[f"{p}.v_proj.weight"].T + w[f"{p}.v_proj.bias"]).view(T, 1, 16)
     o = plain.attention(q, k, v, 0.25, 6)
     x = x + o.reshape(T, 48) @ w[f"{p}.o_proj.weight"].T
-    n = plain.rmsnorm(x, w["model.layers.0.post_attention_layernorm.weight"], 1e-5)
+    n = _centered(x, w["model.layers.0.post_attention_layernorm.weight"],
+                  w["model.layers.0.post_attention_layernorm.bias"], 1e-3)
     y = torch.empty_like(n)
     for t in range(T):
         y[t] = w[f"model.layers.0.mlp.experts.{t % 2}.weight"] @ n[t]
     x = x + y
-    n = plain.rmsnorm(x, w["model.norm.weight"], 1e-5)
+    n = _centered(x, w["model.norm.weight"], w["model.norm.bias"], 1e-3)
     return n @ w["lm_head.weight"].T
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_toy_position_encoding_and_routed_feed_forward(tmp_path, dtype):
+def test_toy_position_encoding_routed_feed_forward_and_norm(tmp_path, dtype):
     register_part("position", "toy_learned_offset", LearnedOffsetEncoding)
     register_part("feed_forward", "toy_parity_routed", ParityRoutedFeedForward)
+    register_part("norm", "toy_centered", CenteredNorm)
     register_architecture(
         "ToyRoutedForCausalLM",
         lambda obj, where: SimpleNamespace(hidden=obj["hidden_size"], vocab=obj["vocab_size"],
@@ -633,6 +672,7 @@ def test_toy_position_encoding_and_routed_feed_forward(tmp_path, dtype):
         _, w = plain.read_model_folder(d)
         assert "model.layers.0.self_attn.position_table" in w
         assert "model.layers.0.mlp.experts.1.weight" in w and "lm_head.weight" in w
+        assert "model.norm.bias" in w and "model.layers.0.post_attention_layernorm.bias" in w
         reqs = mc.make_requests({"vocab_size": 61}, [11, 40, 3, 26], 5)
         ref = {}
         for rid, toks in reqs.items():
@@ -647,6 +687,7 @@ def test_toy_position_encoding_and_routed_feed_forward(tmp_path, dtype):
     finally:
         unregister_part("position", "toy_learned_offset")
         unregister_part("feed_forward", "toy_parity_routed")
+        unregister_part("norm", "toy_centered")
         arch_registry._ARCHITECTURES.pop("ToyRoutedForCausalLM", None)
 
 
