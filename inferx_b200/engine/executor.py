@@ -162,6 +162,7 @@ class Executor:
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
         self._graphs = GraphCache()
         self._graph_pool = None
+        self._capture_stream = None
         self.graph_replays = 0
         self.graph_captures = 0
         self.eager_steps = 0
@@ -394,8 +395,7 @@ class Executor:
             # One memory pool for all recorded steps: they run one after the other, so
             # their activations can live in the same memory; a step's logits stay
             # allocated while its graph is kept and are not handed to a later recording.
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                logits = self.model.forward(ctx, self.caches, rows)
+            logits = self._record(graph, lambda: self.model.forward(ctx, self.caches, rows))
             slot = _Graph(graph, dev, [host, torch.zeros_like(host).pin_memory()], [None, None],
                           logits)
             self._graphs.put(key, slot, decode)
@@ -414,6 +414,25 @@ class Executor:
         slot.graph.replay()
         self.graph_replays += 1
         return slot.logits
+
+    def _record(self, graph, run):
+        """Record ``run()`` into ``graph`` on a stream of its own.  This is what
+        ``torch.cuda.graph`` does, without the garbage collection and the emptying of the
+        allocator's cache that it starts with: a serving run records a few dozen step
+        shapes while it runs, and those two cost more than the recording itself (and the
+        emptied cache makes the next eager steps allocate from the driver again)."""
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(self.device)
+        side, main = self._capture_stream, torch.cuda.current_stream(self.device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            graph.capture_begin(pool=self._graph_pool)
+            try:
+                out = run()
+            finally:
+                graph.capture_end()
+        main.wait_stream(side)
+        return out
 
     # ------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
