@@ -75,7 +75,9 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs.  It is
+    started ahead of the region (the tool takes a moment to come up) and keeps the samples
+    that arrive between ``begin()`` and ``stop()``."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -83,12 +85,16 @@ class ClockSampler:
     def __init__(self):
         self.rows = []
         self.proc = None
+        self.t_begin = None
+
+    def begin(self):
+        self.t_begin = time.perf_counter()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -97,11 +103,12 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.perf_counter(), [x.strip() for x in line.split(",")]))
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        t_end = time.perf_counter()
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -109,7 +116,9 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        t0 = self.t_begin if self.t_begin is not None else 0.0
+        inside = [r for t, r in self.rows if t0 <= t <= t_end]
+        for r in inside:
             if len(r) < 7:
                 continue
             try:
@@ -209,13 +218,15 @@ def time_decode(rt, batch, context, steps, warmup, seed=0, sampler_clock=None):
             mgr.advance(r, 1)
         return ids
 
+    if sampler_clock:
+        sampler_clock.start()
     for i in range(warmup):
         one(i)
     torch.cuda.synchronize()
     l0, c0 = ops.LAUNCHES[0], ops.LIBRARY_CALLS[0]
     r0 = rt.executor.graph_replays
     if sampler_clock:
-        sampler_clock.start()
+        sampler_clock.begin()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for i in range(warmup, warmup + steps):
@@ -541,14 +552,14 @@ def marginal(rt, batch, context, steps):
     return "\n".join(lines)
 
 
-def serving(args):
+def serving_run(args):
     """Continuous batching under memory pressure, in the shape of BASELINE.json's fifth
     configuration: A2.7B layer sizes with every second layer dense, renormalised top-k
     and a sliding window on the last three layers; requests with prompts of uniform random
     length, a fixed number of decoded tokens each, prefill portions of 512 tokens beside
     decoding sequences, and a cache pool sized to a fraction of what the requests would
-    need at once, so that sequences are preempted and recomputed.  Prints one JSON line
-    of its own (tokens per second, steps, preemptions)."""
+    need at once, so that sequences are preempted and recomputed.  Returns the record
+    (tokens per second, steps, preemptions) that ``--serving`` prints."""
     import torch
     from inferx_b200 import Engine, EngineConfig, Request, SamplingParams
     layers = args.layers
@@ -585,7 +596,9 @@ def serving(args):
     reasons = {}
     for c in outs:
         reasons[c.reason] = reasons.get(c.reason, 0) + 1
-    print(json.dumps({
+    del eng
+    torch.cuda.empty_cache()
+    return {
         "workload": "serving", "requests": n_req, "max_num_seqs": args.max_num_seqs,
         "warmup_requests": 1,
         "prompt_tokens": sum(lens), "generated_tokens": st["tokens_generated"],
@@ -598,7 +611,11 @@ def serving(args):
         "capture_seconds": st["capture_seconds"], "eager_steps": st["eager_steps"],
         "host_share_not_waiting": round(1.0 - st["host_seconds"]["wait"] / dt, 3),
         "pool_pages": pages, "pool_fraction_of_demand": args.pool_fraction,
-        "finish_reasons": reasons, "layers": layers, "layers_of_config": FULL_LAYERS}))
+        "finish_reasons": reasons, "layers": layers, "layers_of_config": FULL_LAYERS}
+
+
+def serving(args):
+    print(json.dumps(serving_run(args)))
     return 0
 
 
@@ -842,6 +859,12 @@ def main(argv=None):
                                     "engine is not made at these sizes"}
     if not args.skip_points and args.sizes == "a2.7b":
         out["points"].update(fp32_points(cfg, B, C, hbm_peak))
+    if not args.skip_points and args.sizes == "a2.7b" and args.layers == full_layers:
+        sv = serving_run(args)
+        out["points"].update({"serving_total_tok_s": sv["total_tok_s"],
+                              "serving_seconds": sv["seconds"],
+                              "serving_requests": sv["requests"],
+                              "serving_preemptions": sv["preemptions"]})
     print(json.dumps(out))
     return 0
 
