@@ -429,8 +429,13 @@ class Executor:
             graph.capture_begin(pool=self._graph_pool)
             try:
                 out = run()
-            finally:
-                graph.capture_end()
+            except BaseException:
+                try:                 # leave capture mode, then report what went wrong
+                    graph.capture_end()
+                except Exception:
+                    pass
+                raise
+            graph.capture_end()
         main.wait_stream(side)
         return out
 
