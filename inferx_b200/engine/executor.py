@@ -25,6 +25,7 @@ advances the request's length after the step.
 from __future__ import annotations
 
 import time
+import warnings
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
@@ -431,7 +432,9 @@ class Executor:
                 out = run()
             except BaseException:
                 try:                 # leave capture mode, then report what went wrong
-                    graph.capture_end()
+                    with warnings.catch_warnings():
+                        warnings.simplefilter("ignore")      # "the graph is empty"
+                        graph.capture_end()
                 except Exception:
                     pass
                 raise

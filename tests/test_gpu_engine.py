@@ -222,6 +222,48 @@ def test_a_wait_that_ran_out_is_reported(tmp_path):
     assert int(st.item()) == 0
 
 
+def test_a_step_that_fails_while_recorded_reports_itself_and_leaves_the_executor_usable(tmp_path):
+    """A decode shape is recorded into a CUDA graph the second time it is seen.  If the
+    model's forward pass raises during that recording, the caller gets that error (not one
+    about a capture left open), the stream is out of capture mode, and the same executor
+    goes on: eagerly at once, and recording the shape the next time."""
+    cfg = TINY_A
+    d = mc.make_model_dir(cfg, tmp_path / "m", 2, dtype="float32")
+    reqs = mc.make_requests(cfg, [30], 3)
+    ref = mc.reference_rows(d, reqs)
+    toks = reqs["r0"]
+    sess = ReplaySession(d, "float32", 64, page_size=8, max_live=1, use_graphs=True)
+    ex = sess.executor
+    rows = {}
+
+    def feed(i, lo, hi):
+        out = sess.run_step({"step": i, "entries": [{"id": "r0", "tokens": toks[lo:hi],
+                                                     "want": [hi - lo - 1]}], "end": []})
+        rows[("r0", hi - 1)] = out[0].float().cpu()
+
+    feed(0, 0, 20)
+    feed(1, 20, 21)                      # the decode shape's first sighting: eager
+    orig = ex.model.forward
+
+    def failing(ctx, caches, logit_rows):
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("this part cannot be recorded")
+        return orig(ctx, caches, logit_rows)
+
+    ex.model.forward = failing
+    captures = ex.graph_captures
+    with pytest.raises(RuntimeError, match="this part cannot be recorded"):
+        feed(2, 21, 22)                  # second sighting: recorded, and fails there
+    assert not torch.cuda.is_current_stream_capturing()
+    assert ex.graph_captures == captures and len(ex._graphs) == 0
+    ex.model.forward = orig
+    torch.zeros(4, device="cuda").sum().item()          # the device takes ordinary work
+    for i in range(22, 30):              # the token that failed was not committed: again
+        feed(i, i - 1, i)
+    assert ex.graph_captures == captures + 1 and ex.graph_replays >= 6
+    mc.compare(rows, ref, mc.bound_for("float32", d, reqs), "after a failed recording")
+
+
 def test_command_line(tmp_path):
     cfg = dict(TINY_A, eos_token_id=5)
     d = mc.make_model_dir(cfg, tmp_path / "m", 0)
