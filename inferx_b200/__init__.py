@@ -15,7 +15,7 @@ def __getattr__(name):
     if name == "SamplingParams":
         from .sampling.params import SamplingParams
         return SamplingParams
-    if name in ("Completion", "TokenDelta"):
+    if name in ("Completion", "TokenDelta", "TokenLogprob"):
         from .engine import scheduler as _s
         return getattr(_s, name)
     raise AttributeError(name)

@@ -49,6 +49,13 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--top-k", type=int, default=0)
     ap.add_argument("--min-p", type=float, default=0.0)
+    ap.add_argument("--presence-penalty", type=float, default=0.0)
+    ap.add_argument("--frequency-penalty", type=float, default=0.0)
+    ap.add_argument("--repetition-penalty", type=float, default=1.0)
+    ap.add_argument("--min-tokens", type=int, default=0,
+                    help="stop tokens cannot be chosen before this many were generated")
+    ap.add_argument("--logprobs", type=int, default=None, metavar="K",
+                    help="report each token's log-probability and K alternatives (0 to 20)")
     ap.add_argument("--ignore-eos", action="store_true")
     ap.add_argument("--stop-token-ids", default="", help="token ids that end a request")
     return ap
@@ -95,12 +102,23 @@ def main(argv=None) -> int:
     params = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature,
                             top_p=args.top_p, top_k=args.top_k, min_p=args.min_p,
                             ignore_eos=args.ignore_eos, seed=args.seed,
-                            stop_tokens=tuple(_parse_ids(args.stop_token_ids)))
+                            stop_tokens=tuple(_parse_ids(args.stop_token_ids)),
+                            presence_penalty=args.presence_penalty,
+                            frequency_penalty=args.frequency_penalty,
+                            repetition_penalty=args.repetition_penalty,
+                            min_tokens=args.min_tokens,
+                            want_logprobs=args.logprobs is not None,
+                            top_logprobs=args.logprobs or 0)
     t0 = time.time()
     done = engine.generate([Request(p, params) for p in prompts])
     dt = time.time() - t0
     for i, c in enumerate(done):
-        print(json.dumps({"index": i, "output_ids": c.output_tokens, "finish_reason": c.reason}))
+        rec = {"index": i, "output_ids": c.output_tokens, "finish_reason": c.reason}
+        if c.logprobs is not None:
+            rec["logprobs"] = [{"token": lp.token, "logprob": round(lp.logprob, 6),
+                                "top": [[t, round(p, 6)] for t, p in lp.top]}
+                               for lp in c.logprobs]
+        print(json.dumps(rec))
     if not quiet:
         st = engine.stats()
         print(f"[inferx-generate] {st['tokens_generated']} tokens in {dt:.2f}s, {st['steps']} steps, "

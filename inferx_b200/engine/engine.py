@@ -24,7 +24,7 @@ from ..sampling.sampler import Sampler
 from ..weights.loader import RandomSource
 from .executor import StepEntry
 from .runtime import Runtime, load_model, parse_dtype
-from .scheduler import Completion, Scheduler, SchedulerConfig, TokenDelta
+from .scheduler import Completion, Scheduler, SchedulerConfig, TokenDelta, TokenLogprob
 
 
 @dataclass
@@ -184,11 +184,13 @@ class Engine:
         sampled: List[int] = []
         rows = [e for e in planned if e.sample]
         ids = self.sampler(logits, rows) if rows else None
+        lps = self.sampler.logprobs(logits, ids, rows) if rows else None
         t2 = clock()
         if ids is not None:
             sampled = ids.tolist()          # the one wait of the step
+        records = self._logprob_records(sampled, lps) if lps is not None else None
         t3 = clock()
-        deltas = self.scheduler.commit_step(sampled)
+        deltas = self.scheduler.commit_step(sampled, records)
         t4 = clock()
         sec = self.seconds
         sec["plan"] += t1 - t0
@@ -198,6 +200,22 @@ class Engine:
         self.tokens_generated += len(sampled)
         self.tokens_prefilled += sum(len(e.tokens) for e in planned) - len(rows)
         return deltas
+
+    @staticmethod
+    def _logprob_records(sampled, lps):
+        chosen_lp, top_ids, top_lps, ks = lps
+        chosen_lp = chosen_lp.tolist()
+        top_ids = top_ids.tolist() if top_ids is not None else None
+        top_lps = top_lps.tolist() if top_lps is not None else None
+        out = []
+        for i, k in enumerate(ks):
+            if k < 0:
+                out.append(None)
+                continue
+            top = [(int(t), float(p)) for t, p in zip(top_ids[i][:k], top_lps[i][:k])
+                   if t >= 0] if k > 0 else []
+            out.append(TokenLogprob(int(sampled[i]), float(chosen_lp[i]), top))
+        return out
 
     def stream(self) -> Iterator[TokenDelta]:
         """Run until nothing is left, yielding each token as it is produced."""

@@ -27,12 +27,18 @@ ids, exactly the split of the reference (include/inferx/scheduler/scheduler.h:
   finishes with ``stop_token``, ``max_tokens`` generated with ``max_tokens``.
 * seeds: the row's seed is ``seed ^ (0x9e3779b97f4a7c15 * len(tokens))``
   (scheduler.cc:613-615), so a draw depends on the position, not on the batch.
+* penalties (scheduler.cc:617-645): a row whose request has a penalty carries the distinct
+  tokens it has generated with their counts, most recent first, at most 256 of them (the
+  counts cover the whole generation also when the set is cut).  ``min_tokens``
+  (647-657): while fewer have been generated the row carries its stop tokens (16 at most)
+  to be masked.  Log-probabilities (659-664): -1 when not wanted, else how many
+  alternatives (20 at most); ``commit_step`` attaches them to the tokens.
 """
 from __future__ import annotations
 
 import collections
 from dataclasses import dataclass
-from typing import Deque, Hashable, List, Optional, Sequence
+from typing import Deque, Hashable, List, Optional, Sequence, Tuple
 
 from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
@@ -54,11 +60,26 @@ class SchedulerConfig:
     max_prefill_chunk: int = 0      # per-prompt cap per step; 0 = the budget only
 
 
+PENALTY_HISTORY_CAP = 256       # distinct generated tokens a row's penalties look at
+MASK_CAP = 16                   # stop tokens masked under min_tokens
+MAX_TOP_LOGPROBS = 20
+
+
+@dataclass
+class TokenLogprob:
+    """Of one generated token: its log-probability and the most probable alternatives
+    (token id, log-probability), most probable first."""
+    token: int
+    logprob: float
+    top: List[Tuple[int, float]]
+
+
 @dataclass
 class Completion:
     id: Hashable
     output_tokens: List[int]
     reason: str
+    logprobs: Optional[List[TokenLogprob]] = None     # when the request asked for them
 
 
 @dataclass
@@ -66,6 +87,7 @@ class TokenDelta:
     id: Hashable
     token: int
     finish: Optional[str] = None
+    logprob: Optional[TokenLogprob] = None
 
 
 @dataclass
@@ -78,6 +100,12 @@ class PlannedEntry:
     top_k: int = 0
     min_p: float = 0.0
     seed: int = 0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    history: Tuple[Tuple[int, int], ...] = ()   # (token, count) generated so far, newest first
+    masked: Tuple[int, ...] = ()                # tokens that must not be chosen in this step
+    logprobs_k: int = -1                        # -1: none; else how many alternatives
 
 
 @dataclass
@@ -88,6 +116,7 @@ class _Sequence:
     params: SamplingParams
     cached: int = 0
     cancelled: bool = False
+    logprobs: Optional[List[TokenLogprob]] = None
 
     def pending(self) -> int:
         return len(self.tokens) - self.cached
@@ -137,7 +166,8 @@ class Scheduler:
 
     # -- internals -------------------------------------------------------------
     def _retire(self, seq: _Sequence, reason: str) -> None:
-        self.completed.append(Completion(seq.id, seq.tokens[seq.prompt_len:], reason))
+        self.completed.append(Completion(seq.id, seq.tokens[seq.prompt_len:], reason,
+                                         seq.logprobs))
         if self.cache.has(seq.id):
             self.cache.close(seq.id)
         self._ids.discard(seq.id)
@@ -247,20 +277,48 @@ class Scheduler:
                 continue
             last = seq.cached + n == len(seq.tokens)
             p = seq.params
-            self._planned.append(PlannedEntry(
+            entry = PlannedEntry(
                 id=seq.id, tokens=seq.tokens[seq.cached:seq.cached + n], sample=last,
                 temperature=p.temperature, top_p=p.top_p, top_k=p.top_k, min_p=p.min_p,
-                seed=(p.seed ^ ((0x9E3779B97F4A7C15 * len(seq.tokens)) & _MASK64)) & _MASK64))
+                seed=(p.seed ^ ((0x9E3779B97F4A7C15 * len(seq.tokens)) & _MASK64)) & _MASK64)
+            if last:
+                self._sampling_extras(entry, seq)
+            self._planned.append(entry)
             self._planned_seqs.append(seq)
         self.steps += 1
         return self._planned
 
-    def commit_step(self, sampled: Sequence[int]) -> List[TokenDelta]:
+    @staticmethod
+    def _sampling_extras(entry: PlannedEntry, seq: _Sequence) -> None:
+        p = seq.params
+        if (p.presence_penalty != 0.0 or p.frequency_penalty != 0.0
+                or p.repetition_penalty != 1.0) and seq.generated() > 0:
+            entry.presence_penalty = p.presence_penalty
+            entry.frequency_penalty = p.frequency_penalty
+            entry.repetition_penalty = p.repetition_penalty
+            counts = collections.Counter(seq.tokens[seq.prompt_len:])
+            newest_first = []
+            for tok in reversed(seq.tokens[seq.prompt_len:]):
+                if tok in counts and len(newest_first) < PENALTY_HISTORY_CAP:
+                    newest_first.append((tok, counts.pop(tok)))
+            entry.history = tuple(newest_first)
+        if seq.generated() < p.min_tokens:
+            entry.masked = tuple(p.stop_tokens[:MASK_CAP])
+        if p.want_logprobs:
+            entry.logprobs_k = min(int(p.top_logprobs), MAX_TOP_LOGPROBS)
+
+    def commit_step(self, sampled: Sequence[int],
+                    logprobs: Optional[Sequence[Optional[TokenLogprob]]] = None
+                    ) -> List[TokenDelta]:
         """Record that the planned batch ran; ``sampled`` holds one token per entry
-        that asked for a sample, in entry order."""
+        that asked for a sample, in entry order, and ``logprobs`` (when given) what goes
+        with each of them, None for rows that did not ask."""
         want = sum(1 for e in self._planned if e.sample)
         if len(sampled) != want:
             raise ValueError(f"{len(sampled)} sampled tokens for {want} rows that asked")
+        if logprobs is not None and len(logprobs) != want:
+            raise ValueError(f"{len(logprobs)} log-probability records for {want} rows")
+        lp_it = iter(logprobs) if logprobs is not None else None
         deltas: List[TokenDelta] = []
         finished = []
         it = iter(sampled)
@@ -272,12 +330,18 @@ class Scheduler:
                 continue
             tok = int(next(it))
             seq.tokens.append(tok)
+            lp = next(lp_it) if lp_it is not None else None
+            if lp is not None:
+                if seq.logprobs is None:
+                    seq.logprobs = []
+                # after a preemption the tokens are kept and so are their records
+                seq.logprobs.append(lp)
             reason = None
             if tok in seq.params.stop_tokens:
                 reason = STOP_TOKEN
             elif seq.generated() >= seq.params.max_tokens:
                 reason = MAX_TOKENS
-            deltas.append(TokenDelta(seq.id, tok, reason))
+            deltas.append(TokenDelta(seq.id, tok, reason, lp))
             if reason:
                 finished.append((seq, reason))
         for seq, reason in finished:

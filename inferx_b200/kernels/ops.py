@@ -527,6 +527,63 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
     return out
 
 
+def apply_penalties(logits: torch.Tensor, hist_ids: Optional[torch.Tensor],
+                    hist_counts: Optional[torch.Tensor], penalties: Optional[torch.Tensor],
+                    mask_ids: Optional[torch.Tensor]) -> None:
+    """Penalties and masks on fp32 logits [R,V], in place, before a token is chosen:
+    ``hist_ids`` / ``hist_counts`` [R,H] int32 (distinct generated ids and how often, -1
+    padded) with ``penalties`` [R,3] (presence, frequency, repetition), and ``mask_ids``
+    [R,M] int32 (tokens set to -inf, -1 padded); either group may be absent."""
+    _chk("logits", logits, torch.float32)
+    _chk("hist_ids", hist_ids, torch.int32, optional=True)
+    _chk("hist_counts", hist_counts, torch.int32, optional=True)
+    _chk("penalties", penalties, torch.float32, optional=True)
+    _chk("mask_ids", mask_ids, torch.int32, optional=True)
+    R, V = logits.shape
+    if (hist_ids is None) != (hist_counts is None) or (hist_ids is None) != (penalties is None):
+        raise KernelError("apply_penalties: history ids, counts and penalties come together")
+    if hist_ids is not None and (hist_ids.shape != hist_counts.shape or hist_ids.shape[0] != R
+                                 or tuple(penalties.shape) != (R, 3)):
+        raise KernelError("apply_penalties: history or penalties do not match the rows")
+    if mask_ids is not None and mask_ids.shape[0] != R:
+        raise KernelError("apply_penalties: mask does not match the rows")
+    if hist_ids is None and mask_ids is None:
+        return
+    _check(_lib().ix_apply_penalties(
+        _ptr(logits), R, V, _ptr(hist_ids), _ptr(hist_counts),
+        0 if hist_ids is None else hist_ids.shape[1], _ptr(penalties), _ptr(mask_ids),
+        0 if mask_ids is None else mask_ids.shape[1], _stream()), "apply_penalties")
+    _count()
+
+
+def max_top_logprobs() -> int:
+    return int(_lib().ix_logprobs_max_top())
+
+
+def token_logprobs(logits: torch.Tensor, chosen: torch.Tensor,
+                   want_k: Optional[torch.Tensor] = None, top: int = 0):
+    """Log-probabilities under softmax(logits) of the chosen tokens [R] and of each row's
+    ``want_k[r]`` most probable tokens (ties to the lower id; a negative entry skips the
+    row): (chosen_lp [R] fp32, top_ids [R,top] int32 with -1 where unused, top_lps)."""
+    _chk("logits", logits, torch.float32)
+    _chk("chosen", chosen, torch.int32)
+    _chk("want_k", want_k, torch.int32, optional=True)
+    R, V = logits.shape
+    if chosen.numel() != R or (want_k is not None and want_k.numel() != R):
+        raise KernelError("token_logprobs: one chosen token and one count per row")
+    if not 0 <= top <= max_top_logprobs():
+        raise KernelError(f"token_logprobs: at most {max_top_logprobs()} alternatives")
+    dev = logits.device
+    chosen_lp = torch.empty((R,), dtype=torch.float32, device=dev)
+    top_ids = torch.empty((R, top), dtype=torch.int32, device=dev) if top else None
+    top_lps = torch.empty((R, top), dtype=torch.float32, device=dev) if top else None
+    _check(_lib().ix_token_logprobs(_ptr(logits), R, V, _ptr(chosen), _ptr(want_k), top,
+                                    _ptr(chosen_lp), _ptr(top_ids), _ptr(top_lps), _stream()),
+           "token_logprobs")
+    _count()
+    return chosen_lp, top_ids, top_lps
+
+
 def append_kv(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               slots: torch.Tensor):
     """Write dense k, v rows [T,kv_heads,hd] into the paged cache at ``slots``."""

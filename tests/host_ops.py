@@ -201,6 +201,50 @@ def _uniform(seed):
     return (z >> 40) / 16777216.0
 
 
+def apply_penalties(logits, hist_ids, hist_counts, penalties, mask_ids):
+    R, V = logits.shape
+    for r in range(R):
+        if hist_ids is not None:
+            pres, freq, rep = (float(v) for v in penalties[r])
+            if pres != 0.0 or freq != 0.0 or rep != 1.0:
+                for j in range(hist_ids.shape[1]):
+                    t = int(hist_ids[r, j])
+                    if not 0 <= t < V:
+                        continue
+                    v = logits[r, t]
+                    if rep != 1.0:
+                        v = v / rep if v > 0 else v * rep
+                    logits[r, t] = v - pres - freq * float(hist_counts[r, j])
+        if mask_ids is not None:
+            for j in range(mask_ids.shape[1]):
+                t = int(mask_ids[r, j])
+                if 0 <= t < V:
+                    logits[r, t] = float("-inf")
+
+
+def max_top_logprobs():
+    return 20
+
+
+def token_logprobs(logits, chosen, want_k=None, top=0):
+    R, V = logits.shape
+    chosen_lp = torch.zeros(R, dtype=torch.float32)
+    top_ids = torch.full((R, top), -1, dtype=torch.int32) if top else None
+    top_lps = torch.zeros((R, top), dtype=torch.float32) if top else None
+    for r in range(R):
+        k = int(want_k[r]) if want_k is not None else 0
+        if k < 0:
+            continue
+        row = logits[r].to(torch.float64)
+        log_z = torch.log(torch.exp(row - row.max()).sum()) + row.max()
+        chosen_lp[r] = float(row[int(chosen[r])] - log_z)
+        order = sorted(range(V), key=lambda i: (-float(row[i]), i))[:min(k, top)]
+        for j, i in enumerate(order):
+            top_ids[r, j] = i
+            top_lps[r, j] = float(row[i] - log_z)
+    return chosen_lp, top_ids, top_lps
+
+
 def sample(logits, temperature=None, seeds=None, top_p=None, top_k=None, min_p=None, out=None):
     R, V = logits.shape
     ids = torch.zeros(R, dtype=torch.int32)

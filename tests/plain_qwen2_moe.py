@@ -286,3 +286,33 @@ def sample_temperature(logits_row, temperature, seed):
     c = torch.cumsum(p, 0)
     idx = int(torch.searchsorted(c, torch.tensor(target, dtype=torch.float64)).item())
     return min(idx, len(p) - 1), c, target
+
+
+def penalised(logits_row, generated, presence, frequency, repetition, masked=()):
+    """The logits a token is chosen from when its request has penalties
+    (src/engine/host_sampling.cc:21-48): for every distinct token generated so far,
+    x / repetition when positive else x * repetition, then minus presence, minus
+    frequency times how often it was generated; masked tokens (stop tokens under
+    ``min_tokens``, src/scheduler/scheduler.cc:647-657) end at -inf."""
+    row = logits_row.clone().to(torch.float32)
+    counts = {}
+    for t in generated:
+        counts[t] = counts.get(t, 0) + 1
+    for t, n in counts.items():
+        v = row[t]
+        if repetition != 1.0:
+            v = v / repetition if v > 0 else v * repetition
+        row[t] = v - presence - frequency * n
+    for t in masked:
+        row[t] = float("-inf")
+    return row
+
+
+def logprobs(logits_row, chosen, k):
+    """(log-probability of ``chosen``, [(token, log-probability)] of the k most probable,
+    ties to the lower id) under softmax of the row at temperature 1
+    (src/engine/host_sampling.cc:114-146)."""
+    row = logits_row.to(torch.float64)
+    log_z = float(torch.log(torch.exp(row - row.max()).sum()) + row.max())
+    order = sorted(range(len(row)), key=lambda i: (-float(row[i]), i))[:k]
+    return float(row[chosen]) - log_z, [(i, float(row[i]) - log_z) for i in order]

@@ -90,3 +90,68 @@ def test_host_mirrors_of_a_step_are_shape_or_value(tmp_path):
     assert recorded.kv_lens is None and recorded.state_slots is None
     assert all(g.first_live is None for g in recorded.groups)
     assert recorded.kv_len.tolist() == [31, 8]          # the device's copies are always there
+
+
+def _check_penalised_generation(d, reqs, params, outs):
+    """Every generated token against the plain model: the argmax (ties to the lower id) of
+    the plain logits after the request's penalties over what it had generated so far and
+    after masking its stop tokens under ``min_tokens``; and the reported log-probabilities
+    against the plain ones of that same row."""
+    import plain_qwen2_moe as plain
+    pcfg, w = plain.read_model_folder(d)
+    for toks, p, c in zip(reqs.values(), params, outs):
+        lg = plain.forward(pcfg, w, list(toks) + c.output_tokens)
+        scale = float(lg.abs().max())
+        assert c.logprobs is None or len(c.logprobs) == len(c.output_tokens)
+        for j, got in enumerate(c.output_tokens):
+            generated = c.output_tokens[:j]
+            masked = p.stop_tokens if j < p.min_tokens else ()
+            row = plain.penalised(lg[len(toks) + j - 1], generated, p.presence_penalty,
+                                  p.frequency_penalty, p.repetition_penalty, masked)
+            want = plain.greedy(row)
+            if got != want:        # level within the 32-bit bound, else a fault
+                assert abs(float(row[got] - row[want])) <= 2e-5 * scale, (j, got, want)
+            assert got not in masked
+            if p.want_logprobs:
+                lp = c.logprobs[j]
+                ref_lp, ref_top = plain.logprobs(row, got, p.top_logprobs)
+                assert lp.token == got and abs(lp.logprob - ref_lp) <= 1e-4
+                assert len(lp.top) == p.top_logprobs
+                for (t, v), (rt, rv) in zip(lp.top, ref_top):
+                    assert abs(v - rv) <= 1e-4
+                    assert t == rt or abs(float(row[t] - row[rt])) <= 2e-5 * scale
+
+
+def penalty_workload(cfg):
+    """Requests and sampling options for the penalty tests: greedy, so that every token
+    can be checked against the plain model; one request per feature and one with all."""
+    from inferx_b200 import SamplingParams
+    reqs = mc.make_requests(cfg, [5, 9, 3, 14], 6)
+    vocab = cfg["vocab_size"]
+    stops = (vocab // 2, vocab // 3, 1)
+    params = [SamplingParams(max_tokens=14, repetition_penalty=1.8),
+              SamplingParams(max_tokens=14, presence_penalty=1.5, frequency_penalty=0.7,
+                             want_logprobs=True, top_logprobs=3),
+              SamplingParams(max_tokens=10, want_logprobs=True),
+              SamplingParams(max_tokens=14, repetition_penalty=0.6, frequency_penalty=1.1,
+                             presence_penalty=-0.4, stop_tokens=stops, min_tokens=14,
+                             want_logprobs=True, top_logprobs=5)]
+    return reqs, params
+
+
+@pytest.mark.parametrize("cfg", [TINY_A, TINY_B], ids=["A", "B"])
+def test_penalties_min_tokens_and_logprobs_through_the_engine(tmp_path, cfg):
+    from inferx_b200 import Engine, EngineConfig, Request
+    d = mc.make_model_dir(cfg, tmp_path / "m", 9)
+    reqs, params = penalty_workload(cfg)
+    eng = Engine.create(EngineConfig(model=d, dtype="float32", device="cpu", block_size=4,
+                                     num_gpu_blocks_override=64, max_num_seqs=3,
+                                     prefill_chunk=4, max_model_len=64), ops=host_ops)
+    outs = eng.generate([Request(t, p) for t, p in zip(reqs.values(), params)])
+    assert [len(c.output_tokens) for c in outs] == [14, 14, 10, 14]
+    assert outs[0].logprobs is None and outs[2].logprobs[0].top == []
+    _check_penalised_generation(d, reqs, params, outs)
+    # the penalties do something: without them some request generates other tokens
+    bare = eng.generate([Request(t, type(p)(max_tokens=p.max_tokens))
+                         for t, p in zip(reqs.values(), params)])
+    assert any(a.output_tokens != b.output_tokens for a, b in zip(bare, outs))

@@ -200,6 +200,40 @@ def test_temperature_workload_draws_what_the_plain_sampler_draws(tmp_path):
     assert len({tuple(c.output_tokens) for c in outs}) == 4
 
 
+@pytest.mark.parametrize("dtype,graphs", [("float32", True), ("float32", False),
+                                          ("bfloat16", True)])
+def test_penalties_min_tokens_and_logprobs(tmp_path, dtype, graphs):
+    """Greedy generation with repetition, presence and frequency penalties, stop tokens
+    masked under min_tokens and log-probabilities reported, against the plain model token
+    by token (32-bit), portions of prompts beside decoding rows, recorded steps or not.
+    In bfloat16 the same run must finish, never choose a masked token, and report
+    log-probabilities that are those of its own tokens (at most 0, the chosen one among
+    the alternatives when it is the most probable)."""
+    from test_engine_on_host_double import _check_penalised_generation, penalty_workload
+    cfg = TINY_B
+    d = mc.make_model_dir(cfg, tmp_path / "m", 9,
+                          dtype="float32" if dtype == "float32" else "bfloat16")
+    reqs, params = penalty_workload(cfg)
+    eng = Engine.create(EngineConfig(model=d, dtype=dtype, block_size=4,
+                                     num_gpu_blocks_override=64, max_num_seqs=3,
+                                     prefill_chunk=4, max_model_len=64,
+                                     enforce_eager=not graphs))
+    outs = eng.generate([Request(t, p) for t, p in zip(reqs.values(), params)])
+    assert [len(c.output_tokens) for c in outs] == [14, 14, 10, 14]
+    if dtype == "float32":
+        _check_penalised_generation(d, reqs, params, outs)
+    for p, c in zip(params, outs):
+        assert not set(c.output_tokens[:p.min_tokens]) & set(p.stop_tokens)
+        if p.want_logprobs:
+            for tok, lp in zip(c.output_tokens, c.logprobs):
+                assert lp.token == tok and lp.logprob <= 1e-6 and len(lp.top) == p.top_logprobs
+                if lp.top:
+                    assert lp.top[0][1] >= lp.logprob - 1e-6
+                    assert all(a[1] >= b[1] for a, b in zip(lp.top, lp.top[1:]))
+        else:
+            assert c.logprobs is None
+
+
 def test_a_wait_that_ran_out_is_reported(tmp_path):
     """Kernels with bounded waits write a code into a status word instead of hanging.
     The word is written from the host here (no kernel is made to wait): reading it must
@@ -279,3 +313,17 @@ def test_command_line(tmp_path):
     assert lines[0]["output_ids"] == _plain_greedy(d, [5, 17, 3, 200, 41], 6)
     assert lines[1]["output_ids"] == _plain_greedy(d, [9, 8, 7], 6)
     assert lines[0]["finish_reason"] == "max_tokens"
+    assert "logprobs" not in lines[0]
+    # the sampling options beyond temperature: penalties, min-tokens, log-probabilities
+    p = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "inferx-generate"), d, "--dtype", "fp32",
+         "--block-size", "4", "--max-model-len", "64", "--num-gpu-blocks-override", "32",
+         "--prompt-ids", "9 8 7", "--max-tokens", "5", "--repetition-penalty", "1.5",
+         "--presence-penalty", "0.3", "--frequency-penalty", "0.2", "--min-tokens", "5",
+         "--stop-token-ids", "5,6", "--logprobs", "2", "--log-level", "warning"],
+        capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    (line,) = [json.loads(ln) for ln in p.stdout.splitlines() if ln.startswith("{")]
+    assert len(line["output_ids"]) == 5 and not set(line["output_ids"]) & {5, 6}
+    assert [lp["token"] for lp in line["logprobs"]] == line["output_ids"]
+    assert all(len(lp["top"]) == 2 and lp["logprob"] <= 0 for lp in line["logprobs"])

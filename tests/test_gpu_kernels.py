@@ -804,3 +804,81 @@ def test_paged_attention_tiled(dtype, heads, kvh, hd, page, window):
         torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-5)
     else:
         _close(out.cpu(), ref, dtype)
+
+
+@pytest.mark.parametrize("R,V,H,M", [(1, 97, 5, 2), (4, 1000, 256, 16), (3, 151936, 40, 3)])
+def test_apply_penalties(R, V, H, M):
+    """Penalties over a row's distinct generated tokens and the mask under min_tokens,
+    against the plain statement; rows whose penalties are neutral, padding ids, ids past
+    the vocabulary and a token that is both penalised and masked."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(R * V)
+    logits = torch.randn(R, V, generator=g) * 4
+    ids = torch.full((R, H), -1, dtype=torch.int32)
+    counts = torch.zeros((R, H), dtype=torch.int32)
+    pen = torch.tensor([[0.0, 0.0, 1.0]] * R)
+    mask = torch.full((R, M), -1, dtype=torch.int32)
+    for r in range(R):
+        n = int(torch.randint(1, H + 1, (1,), generator=g))
+        ids[r, :n] = torch.randperm(V, generator=g)[:n].to(torch.int32)
+        counts[r, :n] = torch.randint(1, 9, (n,), generator=g).to(torch.int32)
+        if r != 1:                              # row 1 keeps neutral penalties
+            pen[r] = torch.tensor([0.7, 0.3, 1.6]) if r % 2 == 0 else torch.tensor([-0.5, 0.0, 0.8])
+        if r % 2 == 0:
+            mask[r, 0] = ids[r, 0]              # penalised and masked: masked wins
+            if M > 1:
+                mask[r, 1] = V - 1
+    if H > 3:
+        ids[0, 2] = V + 5                       # past the vocabulary: ignored
+    ref = logits.clone()
+    host_ops.apply_penalties(ref, ids, counts, pen, mask)
+    out = logits.clone().cuda()
+    ops.apply_penalties(out, ids.cuda(), counts.cuda(), pen.cuda(), mask.cuda())
+    # to rounding: the device contracts the frequency term into one multiply-add
+    torch.testing.assert_close(out.cpu(), ref, rtol=1e-6, atol=1e-6)
+    untouched = ref == logits
+    assert torch.equal(out.cpu()[untouched], logits[untouched])
+    assert torch.isinf(ref[0, int(mask[0, 0])]) and (ref != logits).any()
+    only_mask = logits.clone().cuda()
+    ops.apply_penalties(only_mask, None, None, None, mask.cuda())
+    ref2 = logits.clone()
+    host_ops.apply_penalties(ref2, None, None, None, mask)
+    assert torch.equal(only_mask.cpu(), ref2)
+
+
+@pytest.mark.parametrize("R,V,top", [(2, 97, 5), (5, 1000, 20), (3, 151936, 7), (2, 33, 0)])
+def test_token_logprobs(R, V, top):
+    """log softmax of the chosen token and the most probable alternatives (ties to the
+    lower id) against the plain statement; rows that ask for fewer or for none, tied
+    logits, masked (-inf) entries."""
+    import plain_qwen2_moe as plain
+    ops = _ops()
+    g = torch.Generator().manual_seed(V + top)
+    logits = torch.randn(R, V, generator=g) * 3
+    logits[0, 5] = logits[0, 3] = logits[0].max() + 1.0      # a tie at the top: 3 before 5
+    logits[-1, 7] = float("-inf")
+    chosen = torch.randint(0, V, (R,), generator=g).to(torch.int32)
+    chosen[0] = 5
+    want = torch.tensor([top, -1, max(top - 2, 0), 0, top][:R], dtype=torch.int32)
+    lp, ids, lps = ops.token_logprobs(logits.cuda(), chosen.cuda(), want.cuda(), top)
+    lp = lp.cpu()
+    for r in range(R):
+        k = int(want[r])
+        if k < 0:
+            continue
+        ref_lp, ref_top = plain.logprobs(logits[r], int(chosen[r]), k)
+        assert abs(float(lp[r]) - ref_lp) <= 2e-5 * max(1.0, abs(ref_lp))
+        if top:
+            got_ids, got_lps = ids[r].cpu().tolist(), lps[r].cpu().tolist()
+            assert got_ids[:k] == [t for t, _ in ref_top]
+            assert all(t == -1 for t in got_ids[k:])
+            for a, (_, b) in zip(got_lps[:k], ref_top):
+                assert abs(a - b) <= 2e-5 * max(1.0, abs(b))
+    if top >= 2:
+        assert ids[0, :2].cpu().tolist() == [3, 5]
+    # chosen token only, every row
+    lp_all, none_ids, _ = ops.token_logprobs(logits.cuda(), chosen.cuda())
+    assert none_ids is None
+    for r in range(R):
+        ref_lp, _ = plain.logprobs(logits[r], int(chosen[r]), 0)
+        assert abs(float(lp_all[r]) - ref_lp) <= 2e-5 * max(1.0, abs(ref_lp))

@@ -222,6 +222,63 @@ def test_row_seed_depends_on_position_not_on_batch():
     assert e2.seed == 99 ^ ((0x9E3779B97F4A7C15 * 4) & ((1 << 64) - 1))
 
 
+def test_penalty_history_masks_and_logprob_counts_of_a_row():
+    """A row whose request has a penalty carries the distinct tokens generated so far with
+    their counts, newest first (src/scheduler/scheduler.cc:617-645); under ``min_tokens``
+    it carries its stop tokens to be masked (647-657); the count of alternatives is -1
+    when log-probabilities are not wanted (659-664).  Prompt tokens are no history."""
+    from inferx_b200.engine.scheduler import TokenLogprob
+    s, c = make()
+    s.add_request("a", [7, 7, 9], SamplingParams(max_tokens=8, repetition_penalty=1.3,
+                                                presence_penalty=0.5, stop_tokens=(4, 2),
+                                                min_tokens=2, want_logprobs=True,
+                                                top_logprobs=50))
+    s.add_request("b", [1, 2], SamplingParams(max_tokens=8))
+    a, b = s.prepare_step()
+    assert a.history == () and a.masked == (4, 2) and a.logprobs_k == 20
+    assert b.history == () and b.masked == () and b.logprobs_k == -1
+    assert (a.presence_penalty, a.repetition_penalty) == (0.0, 1.0)     # nothing generated yet
+    deltas = s.commit_step([11, 3], [TokenLogprob(11, -0.5, [(11, -0.5)]), None])
+    assert deltas[0].logprob.logprob == -0.5 and deltas[1].logprob is None
+    for tok in (12, 11, 11):
+        a, b = s.prepare_step()
+        s.commit_step([tok, 3], [TokenLogprob(tok, -1.0, []), None])
+    a, b = s.prepare_step()
+    assert a.history == ((11, 3), (12, 1))            # newest first, counts of the whole run
+    assert (a.presence_penalty, a.frequency_penalty, a.repetition_penalty) == (0.5, 0.0, 1.3)
+    assert a.masked == ()                             # four generated: past min_tokens
+    assert b.history == ()                            # no penalty asked: no history carried
+    s.commit_step([4, 3], [TokenLogprob(4, -2.0, []), None])        # a's stop token
+    done = {x.id: x for x in s.take_completed()}
+    assert done["a"].reason == STOP_TOKEN and done["a"].output_tokens == [11, 12, 11, 11, 4]
+    assert [lp.token for lp in done["a"].logprobs] == [11, 12, 11, 11, 4]
+    with pytest.raises(ValueError):
+        s.prepare_step()
+        s.commit_step([3], [None, None])              # one record per sampled row
+    with pytest.raises(ValueError):
+        SamplingParams(repetition_penalty=0.0)
+    with pytest.raises(ValueError):
+        SamplingParams(min_tokens=-1)
+
+
+def test_penalty_history_is_cut_to_the_newest_distinct_tokens():
+    from inferx_b200.engine.scheduler import PENALTY_HISTORY_CAP
+    s, c = make(pages=400, max_seq_len=2000)
+    s.add_request("a", [1], SamplingParams(max_tokens=1000, frequency_penalty=0.1))
+    n = PENALTY_HISTORY_CAP + 40
+    for i in range(n):
+        s.prepare_step()
+        s.commit_step([100 + i])
+    for _ in range(3):
+        s.prepare_step()
+        s.commit_step([100])                          # the oldest token, again
+    (a,) = s.prepare_step()
+    assert len(a.history) == PENALTY_HISTORY_CAP
+    assert a.history[0] == (100, 4)                   # newest first, all four occurrences
+    assert a.history[1] == (100 + n - 1, 1)
+    assert (101, 1) not in a.history                  # the oldest distinct ones fell out
+
+
 def test_commit_checks_the_number_of_samples():
     s, c = make()
     s.add_request("a", [1, 2, 3], SamplingParams())
