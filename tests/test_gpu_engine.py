@@ -320,9 +320,13 @@ def test_command_line(tmp_path):
          "--block-size", "4", "--max-model-len", "64", "--num-gpu-blocks-override", "32",
          "--prompt-ids", "9 8 7", "--max-tokens", "5", "--repetition-penalty", "1.5",
          "--presence-penalty", "0.3", "--frequency-penalty", "0.2", "--min-tokens", "5",
-         "--stop-token-ids", "5,6", "--logprobs", "2", "--log-level", "warning"],
+         "--stop-token-ids", "5,6", "--logprobs", "2", "--log-json", "--log-file",
+         str(tmp_path / "run.log"), "--kv-blocks", "32", "--no-cuda-graphs"],
         capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stderr[-2000:]
+    logged = [json.loads(ln) for ln in (tmp_path / "run.log").read_text().splitlines()]
+    assert [r["level"] for r in logged] == ["info", "info"] and logged[1]["steps"] >= 5
+    assert logged[1]["graph_replays"] == 0            # --no-cuda-graphs
     (line,) = [json.loads(ln) for ln in p.stdout.splitlines() if ln.startswith("{")]
     assert len(line["output_ids"]) == 5 and not set(line["output_ids"]) & {5, 6}
     assert [lp["token"] for lp in line["logprobs"]] == line["output_ids"]
