@@ -199,6 +199,45 @@ def test_layer_sizes_of_the_benchmark_model(tmp_path, dtype):
         print(f"mid/{kind}/{dtype}: worst relative error {worst:.3e}")
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_dependent_launch_changes_no_bit(tmp_path, graphs):
+    """Decode steps of a few tokens are launched so that a kernel may come onto the device
+    while its predecessor drains, and some kernels read what was written two launches back
+    (the experts' row offsets) or ask for their first weights before they wait.  If one of
+    them ever read something too early, a result would differ from the run without such
+    launches; the two runs use the same kernels in the same order, so every logit must be
+    the same bit for bit.  Four mixture layers at the benchmark's widths, 48 steps of four
+    sequences, eagerly and from recorded steps."""
+    from inferx_b200.kernels import ops
+    cfg = dict(MID, num_hidden_layers=4, decoder_sparse_step=1, max_window_layers=2)
+    d = mc.make_model_dir(cfg, tmp_path / "m", 5, dtype="bfloat16")
+    new = 48
+    reqs = mc.make_requests(cfg, [new + 41, new + 33, new + 20, new + 9], 5)
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": t[:len(t) - new], "want": [len(t) - new - 1]}
+                                     for r, t in reqs.items()], "end": []}]
+    for i in range(new):
+        steps.append({"step": i + 1, "entries": [{"id": r, "tokens": [t[len(t) - new + i]],
+                                                   "want": [0]} for r, t in reqs.items()],
+                      "end": list(reqs) if i == new - 1 else []})
+
+    def run():
+        sess = ReplaySession(d, "bfloat16", traces.peak_tokens(steps), page_size=16, max_live=4,
+                             use_graphs=graphs)
+        return [sess.run_step(s).float().cpu() for s in steps]
+
+    limit = ops.DEPENDENT_LAUNCH_MAX_TOKENS
+    assert limit >= 4
+    overlapped = run()
+    try:
+        ops.DEPENDENT_LAUNCH_MAX_TOKENS = 0
+        plain_launches = run()
+    finally:
+        ops.DEPENDENT_LAUNCH_MAX_TOKENS = limit
+    for i, (a, b) in enumerate(zip(overlapped, plain_launches)):
+        assert torch.isfinite(a).all()
+        assert torch.equal(a, b), f"step {i}: dependent launches changed a logit"
+
+
 LONG = {
     "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
     "num_hidden_layers": 2, "hidden_size": 1024, "num_attention_heads": 8,
