@@ -114,6 +114,15 @@ class MoeFeedForward:
     # and at batch 32, where the routed products are persistent tensor-core kernels, 24.7
     # against 25.4 ms).  Swapping the roles there - the shared expert on the main stream,
     # the router's short kernels and the dispatch beside it - measured worse still (20.1 ms).
+    #
+    # Above that many tokens the shared expert still runs on the stream of its own, but it
+    # is handed over later, after the dispatch and just before the routed gate/up product:
+    # at prompt sizes the routed products are bound by reading the experts' weights and
+    # leave the tensor pipe idle, the shared expert's products are bound by the tensor
+    # pipe, and the routed kernels, launched first, keep their places (a prompt portion of
+    # 512 tokens 5.0 against 5.6 ms, 1,024 tokens 7.1 against 7.6 ms, 2,048 tokens 12.26
+    # against 12.55 ms, 8,192 tokens 44.6 against 45.0 ms; handed over first, as below the
+    # bound, 5.5 / 7.2 / 12.1 / 45.5 ms).
     OVERLAP_MAX_TOKENS = 256
     OVERLAP_LARGE_WEIGHT_BYTES = 160 << 20
     OVERLAP_LARGE_NOT_FOR_TOKENS = (3, 16)
@@ -131,16 +140,25 @@ class MoeFeedForward:
 
     def forward(self, x, step=None):
         s, ops = self.spec, self.ctx.ops
-        shared, side = None, None
-        if self.shared is not None and x.is_cuda and self._overlap_shared(x.shape[0]):
+        shared, side, ready = None, None, None
+        beside = self.shared is not None and x.is_cuda
+        if beside and self._overlap_shared(x.shape[0]):
             side = self._side_stream()
             main = torch.cuda.current_stream(x.device)
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 shared = self.shared.forward(x, step)
+        elif beside and x.shape[0] > self.OVERLAP_MAX_TOKENS:
+            side = self._side_stream()
+            main = torch.cuda.current_stream(x.device)
+            ready = main.record_event()        # x is there; what follows is not waited for
         topk_w, topk_idx, shared_logit = ops.router_topk(
             x, self.router_w, s.top_k, s.renormalize, s.routed_scale, extra_w=self.shared_gate_w)
         offsets, rows, dest = ops.moe_dispatch(topk_idx, s.num_experts)
+        if ready is not None:
+            side.wait_event(ready)
+            with torch.cuda.stream(side):
+                shared = self.shared.forward(x, step)
         act = ops.grouped_gate_up_swiglu(x, rows, offsets, self.expert_gate_up)
         # `offsets` was written by the dispatch, two launches back: the down product may
         # start on its weights while the gate/up product drains
