@@ -122,7 +122,10 @@ class MoeFeedForward:
     # pipe, and the routed kernels, launched first, keep their places (a prompt portion of
     # 512 tokens 5.0 against 5.6 ms, 1,024 tokens 7.1 against 7.6 ms, 2,048 tokens 12.26
     # against 12.55 ms, 8,192 tokens 44.6 against 45.0 ms; handed over first, as below the
-    # bound, 5.5 / 7.2 / 12.1 / 45.5 ms).
+    # bound, 5.5 / 7.2 / 12.1 / 45.5 ms).  Not for a large shared expert: what it allocates on
+    # its own stream (gigabytes at 8,192 tokens and 20,480 columns) comes on top of what the
+    # main stream holds, since the allocator keeps a pool per stream, and a model that fills
+    # the device has no room for that.
     OVERLAP_MAX_TOKENS = 256
     OVERLAP_LARGE_WEIGHT_BYTES = 160 << 20
     OVERLAP_LARGE_NOT_FOR_TOKENS = (3, 16)
@@ -148,7 +151,8 @@ class MoeFeedForward:
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 shared = self.shared.forward(x, step)
-        elif beside and x.shape[0] > self.OVERLAP_MAX_TOKENS:
+        elif (beside and x.shape[0] > self.OVERLAP_MAX_TOKENS
+              and self._shared_bytes <= self.OVERLAP_LARGE_WEIGHT_BYTES):
             side = self._side_stream()
             main = torch.cuda.current_stream(x.device)
             ready = main.record_event()        # x is there; what follows is not waited for
