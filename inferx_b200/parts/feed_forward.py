@@ -101,7 +101,7 @@ class MoeFeedForward:
             if s.shared_gated:
                 self.shared_gate_w = w[f"{p}.{s.shared_gate_name}.weight"].reshape(-1).contiguous()
 
-    # Below this many tokens a step's kernels leave the GPU partly idle; the shared
+    # In a step of few tokens the kernels leave the GPU partly idle; the shared
     # expert (which needs nothing from the router) then runs beside the routed experts,
     # on a stream of its own: its products cover the router's short kernels and the
     # boundaries between them (69 MB of shared weights a layer: a decode step of 3.94
@@ -115,7 +115,7 @@ class MoeFeedForward:
     # against 25.4 ms).  Swapping the roles there - the shared expert on the main stream,
     # the router's short kernels and the dispatch beside it - measured worse still (20.1 ms).
     #
-    # Above that many tokens the shared expert still runs on the stream of its own, but it
+    # In larger steps the shared expert still runs on the stream of its own, but it
     # is handed over later, after the dispatch and just before the routed gate/up product:
     # at prompt sizes the routed products are bound by reading the experts' weights and
     # leave the tensor pipe idle, the shared expert's products are bound by the tensor
@@ -126,15 +126,22 @@ class MoeFeedForward:
     # its own stream (gigabytes at 8,192 tokens and 20,480 columns) comes on top of what the
     # main stream holds, since the allocator keeps a pool per stream, and a model that fills
     # the device has no room for that.
+    # Between the two the later hand-over already pays (128 tokens 3.84 against 4.18 ms,
+    # 256 tokens 4.19 against 4.55 ms; 32 tokens and decode steps of 32 and 64 sequences the
+    # same either way), so the early one is kept for steps of at most 16 tokens, and, for a
+    # large shared expert, which is never handed over late, up to 256.
     OVERLAP_MAX_TOKENS = 256
+    EARLY_MAX_TOKENS = 16
     OVERLAP_LARGE_WEIGHT_BYTES = 160 << 20
     OVERLAP_LARGE_NOT_FOR_TOKENS = (3, 16)
 
     def _overlap_shared(self, tokens: int) -> bool:
-        if tokens > self.OVERLAP_MAX_TOKENS:
+        """Whether the shared expert is handed to its stream before the router."""
+        large = self._shared_bytes > self.OVERLAP_LARGE_WEIGHT_BYTES
+        if tokens > (self.OVERLAP_MAX_TOKENS if large else self.EARLY_MAX_TOKENS):
             return False
         lo, hi = self.OVERLAP_LARGE_NOT_FOR_TOKENS
-        return not (self._shared_bytes > self.OVERLAP_LARGE_WEIGHT_BYTES and lo <= tokens <= hi)
+        return not (large and lo <= tokens <= hi)
 
     def _side_stream(self):
         if self._side is None:
@@ -151,7 +158,7 @@ class MoeFeedForward:
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 shared = self.shared.forward(x, step)
-        elif (beside and x.shape[0] > self.OVERLAP_MAX_TOKENS
+        elif (beside and x.shape[0] > self.EARLY_MAX_TOKENS
               and self._shared_bytes <= self.OVERLAP_LARGE_WEIGHT_BYTES):
             side = self._side_stream()
             main = torch.cuda.current_stream(x.device)
