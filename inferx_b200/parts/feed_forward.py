@@ -44,6 +44,9 @@ class SwiGluFeedForward:
         return ops.linear(ops.gate_up_swiglu(x, self.gate_up_w), self.down_w)
 
 
+_SIDE_STREAMS: dict = {}
+
+
 class MoeFeedForward:
     def __init__(self, spec, ctx, prefix: str):
         self.spec, self.ctx, self.prefix = spec, ctx, prefix
@@ -122,10 +125,12 @@ class MoeFeedForward:
     # pipe, and the routed kernels, launched first, keep their places (a prompt portion of
     # 512 tokens 5.0 against 5.6 ms, 1,024 tokens 7.1 against 7.6 ms, 2,048 tokens 12.26
     # against 12.55 ms, 8,192 tokens 44.6 against 45.0 ms; handed over first, as below the
-    # bound, 5.5 / 7.2 / 12.1 / 45.5 ms).  Not for a large shared expert: what it allocates on
-    # its own stream (gigabytes at 8,192 tokens and 20,480 columns) comes on top of what the
-    # main stream holds, since the allocator keeps a pool per stream, and a model that fills
-    # the device has no room for that.
+    # bound, 5.5 / 7.2 / 12.1 / 45.5 ms).  Not for a large shared expert: at the sizes that
+    # have one (64 experts of 2560 x 3584, eight chosen) an expert sees 256 rows of a
+    # 2,048-token portion and the routed products keep the tensor pipe busy themselves
+    # (62.5 against 62.7 ms), while what the shared expert allocates on its own stream (a
+    # gigabyte at 8,192 tokens and 20,480 columns) comes on top of what the main stream
+    # holds, since the allocator keeps a pool per stream.
     # Between the two the later hand-over already pays (128 tokens 3.84 against 4.18 ms,
     # 256 tokens 4.19 against 4.55 ms; 32 tokens and decode steps of 32 and 64 sequences the
     # same either way), so the early one is kept for steps of at most 16 tokens, and, for a
@@ -144,8 +149,15 @@ class MoeFeedForward:
         return not (large and lo <= tokens <= hi)
 
     def _side_stream(self):
+        # One stream per device for all layers: the allocator keeps a pool of memory per
+        # stream, and a stream per layer kept every layer's copy of the shared expert's
+        # activations for itself (7 GB at 8,192 tokens and 24 layers); the layers run one
+        # after the other anyway.
         if self._side is None:
-            self._side = torch.cuda.Stream(device=self.ctx.device)
+            dev = torch.device(self.ctx.device)
+            if dev not in _SIDE_STREAMS:
+                _SIDE_STREAMS[dev] = torch.cuda.Stream(device=dev)
+            self._side = _SIDE_STREAMS[dev]
         return self._side
 
     def forward(self, x, step=None):

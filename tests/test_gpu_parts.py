@@ -107,6 +107,35 @@ def test_moe_part(dtype, renorm, shared, gated):
         _assert_close_scaled(out.float().cpu(), ref, dtype)
 
 
+def test_moe_layers_share_one_side_stream_and_its_memory():
+    """The shared expert runs on a stream beside the routed experts.  The allocator keeps a
+    pool of memory per stream, so that stream is one per device, not one per layer: eight
+    layers stepping 600 tokens reserve about what one layer needs for the shared expert's
+    activations, not eight times that."""
+    ctx = _ctx(torch.bfloat16)
+    spec = MoeSpec(hidden=512, num_experts=8, top_k=2, expert_intermediate=256, renormalize=True,
+                   routed_scale=1.0, shared_gated=True,
+                   shared=SwiGluSpec(hidden=512, intermediate=4096))
+    layers = [build_part("feed_forward", spec, ctx, f"mlp{i}") for i in range(8)]
+    for part in layers:
+        _bind(part, ctx, std=0.05)
+    T = 600
+    x = torch.randn(T, 512).to(torch.bfloat16).cuda()
+    per_layer = T * (2 * 4096 + 4096 + 512) * 2          # gate|up, activation, output
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    before = torch.cuda.memory_reserved()
+    for _ in range(2):
+        for part in layers:
+            out = part.forward(x)
+            if hasattr(out, "materialize"):
+                out = out.materialize()
+    torch.cuda.synchronize()
+    assert len({id(part._side_stream()) for part in layers}) == 1
+    grown = torch.cuda.memory_reserved() - before
+    assert grown < 4 * per_layer + (64 << 20), (grown, per_layer)
+
+
 def _step_context(ctx, mixer, tokens_per_seq, page=4):
     """Cache, storage and a step context for whole sequences through one mixer."""
     needs = [list(mixer.cache_needs())]
