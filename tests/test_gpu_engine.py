@@ -234,6 +234,43 @@ def test_penalties_min_tokens_and_logprobs(tmp_path, dtype, graphs):
             assert c.logprobs is None
 
 
+def test_rounds_of_wandering_requests_leave_nothing_behind(tmp_path):
+    """Three rounds of 24 requests with prompts of wandering lengths and every sampling
+    option in some of them, through one engine whose pool forces preemptions: every request
+    gets exactly its tokens, every page is free again after a round, the recorded step
+    shapes stay within their bounds (old ones are dropped), and the memory the process
+    holds stops growing after the first round."""
+    cfg = dict(TINY_B, num_hidden_layers=3)
+    d = mc.make_model_dir(cfg, tmp_path / "m", 3, dtype="bfloat16")
+    eng = Engine.create(EngineConfig(model=d, dtype="bfloat16", block_size=8, max_num_seqs=12,
+                                     num_gpu_blocks_override=90, prefill_chunk=32,
+                                     max_num_batched_tokens=96, max_model_len=400))
+    vocab = cfg["vocab_size"]
+    reserved = []
+    for rnd in range(3):
+        g = torch.Generator().manual_seed(50 + rnd)
+        lens = torch.randint(1, 200, (24,), generator=g).tolist()
+        prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+        params = [SamplingParams(max_tokens=int(torch.randint(1, 60, (1,), generator=g)),
+                                 ignore_eos=True, temperature=0.8 if i % 3 == 0 else 0.0, seed=i,
+                                 top_k=7 if i % 6 == 0 else 0, top_p=0.9 if i % 7 == 0 else 1.0,
+                                 repetition_penalty=1.2 if i % 4 == 0 else 1.0,
+                                 presence_penalty=0.3 if i % 8 == 0 else 0.0,
+                                 want_logprobs=i % 5 == 0, top_logprobs=2) for i in range(24)]
+        outs = eng.generate([Request(p, q) for p, q in zip(prompts, params)])
+        torch.cuda.synchronize()
+        st = eng.stats()
+        assert [len(c.output_tokens) for c in outs] == [q.max_tokens for q in params]
+        assert all((c.logprobs is not None) == q.want_logprobs for c, q in zip(outs, params))
+        assert st["pages_free"] == st["pages_total"] and st["running"] == st["waiting"] == 0
+        eng.runtime.manager.check_invariants()
+        graphs = eng.runtime.executor._graphs
+        assert graphs.count(True) <= graphs.limits[True] and graphs.count(False) <= graphs.limits[False]
+        reserved.append(torch.cuda.memory_reserved())
+    assert eng.stats()["preemptions"] >= 1 and eng.stats()["graph_replays"] > 100
+    assert reserved[2] <= reserved[0] + (64 << 20), reserved
+
+
 def test_a_wait_that_ran_out_is_reported(tmp_path):
     """Kernels with bounded waits write a code into a status word instead of hanging.
     The word is written from the host here (no kernel is made to wait): reading it must
