@@ -3,8 +3,11 @@
 It rests on the formulas of divedb/InferX's sources, not on running them: the
 reference's model code exists only as CUDA behind abseil/cuBLASLt/FlashInfer,
 which cannot be compiled or imported on the CPU here (its ``third_party/`` is
-empty), so there is no golden output made by the reference itself.  Each function
-below cites the reference lines whose arithmetic it restates.  It shares no code
+empty), so there is no golden output of the forward pass made by the reference itself
+(its scheduler and its host sampler do compile on the CPU: tests/golden/ holds what they
+decide, and tests/test_scheduler_golden.py compares this file's sampling statements and
+the package's scheduler with that).  Each function below cites the reference lines whose
+arithmetic it restates.  It shares no code
 with ``inferx_b200``: it reads config.json as a plain dict and the tensors by
 their checkpoint names from a plain dict of fp32 CPU tensors.
 

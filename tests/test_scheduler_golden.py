@@ -1,0 +1,149 @@
+"""This repository's scheduler and plain sampling statements against the reference's own
+code, run on the CPU: tests/golden/make_golden.sh compiled divedb/InferX's scheduler, block
+pool and host sampler (unmodified, with a small stand-in for abseil) and recorded what they
+decide for a scripted scenario (tests/golden/scheduler_golden.cc, sampling_golden.cc).  The
+records are committed; this test needs neither the reference nor a compiler.
+
+The scenario: nine requests arriving over eleven steps into three running slots, a budget
+of 16 tokens a step, twelve blocks of four tokens (two preemptions), prompts cut into
+portions, penalties, stop tokens under min_tokens, log-probabilities, seeds, a request
+longer than the context, one that fills it, one cancelled."""
+import json
+import os
+
+import pytest
+import torch
+
+import plain_qwen2_moe as plain
+from inferx_b200.cache import CacheGroup, CacheManager
+from inferx_b200.engine.scheduler import Scheduler, SchedulerConfig, TokenLogprob
+from inferx_b200.sampling import SamplingParams
+
+HERE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _records(name):
+    with open(os.path.join(HERE, name)) as f:
+        return [json.loads(line) for line in f if line.strip()]
+
+
+def _prompt(n, salt):
+    return [(salt * 37 + i * 11) % 89 + 5 for i in range(n)]
+
+
+def _arrivals():
+    stops = tuple(range(40, 50))
+    return [
+        (0, 1, _prompt(9, 1), SamplingParams(max_tokens=6)),
+        (0, 2, _prompt(5, 2), SamplingParams(max_tokens=9, temperature=0.7, seed=12345, top_k=5,
+                                             top_p=0.9, min_p=0.05, repetition_penalty=1.3,
+                                             presence_penalty=0.25)),
+        (0, 3, _prompt(20, 3), SamplingParams(max_tokens=5, frequency_penalty=0.5,
+                                              want_logprobs=True, top_logprobs=3)),
+        (3, 4, _prompt(3, 4), SamplingParams(max_tokens=30, stop_tokens=stops, min_tokens=4,
+                                             want_logprobs=True, top_logprobs=40)),
+        (5, 5, _prompt(7, 5), SamplingParams(max_tokens=3)),
+        (8, 6, _prompt(12, 6), SamplingParams(max_tokens=8, seed=0xfedcba9876543210,
+                                              temperature=1.0)),
+        (8, 7, _prompt(45, 7), SamplingParams(max_tokens=4)),
+        (10, 8, _prompt(30, 8), SamplingParams(max_tokens=50)),
+        (11, 9, _prompt(14, 9), SamplingParams(max_tokens=12)),
+    ]
+
+
+def _f32(x):
+    return float(torch.tensor(x, dtype=torch.float32))
+
+
+def test_scheduler_decides_what_the_reference_scheduler_decides():
+    golden = _records("scheduler_golden.jsonl")
+    assert len(golden) == 29 and golden[-1]["preemptions"] == 2
+    cache = CacheManager([CacheGroup(0)], 12, 4, 8)
+    sched = Scheduler(SchedulerConfig(max_running=3, max_batch_tokens=16, max_seq_len=40), cache)
+    arrivals = _arrivals()
+    for rec in golden:
+        step = rec["step"]
+        for at, rid, prompt, params in arrivals:
+            if at == step:
+                sched.add_request(rid, prompt, params)
+        if step == 14:
+            sched.cancel(9)
+        planned = sched.prepare_step()
+        done = sched.take_completed()
+        rows, sampled, records, rows_meta = [], [], [], []
+        for e in planned:
+            start = cache.length(e.id)
+            rows.append([len(e.tokens), start, e.tokens[-1], start + len(e.tokens)])
+            if e.sample:
+                sampled.append((e.tokens[-1] * 31 + (start + len(e.tokens) - 1) * 17) % 97 + 3)
+                rows_meta.append(e)
+        assert rows == rec["rows"], f"step {step}: the batch differs"
+        assert len(rows_meta) == len(rec["sampled_rows"])
+        for i, (e, g) in enumerate(zip(rows_meta, rec["sampled_rows"])):
+            where = f"step {step}, sampled row {i}"
+            assert e.seed == int(g["seed"]), where
+            assert (_f32(e.temperature), _f32(e.top_p), e.top_k, _f32(e.min_p)) == \
+                (_f32(g["temperature"]), _f32(g["top_p"]), g["top_k"], _f32(g["min_p"])), where
+            assert [t for t, _ in e.history] == g["history_ids"], where
+            assert [c for _, c in e.history] == g["history_counts"], where
+            if e.history:       # without history the penalties change nothing on either side
+                assert (_f32(e.presence_penalty), _f32(e.frequency_penalty),
+                        _f32(e.repetition_penalty)) == \
+                    (_f32(g["presence"]), _f32(g["frequency"]), _f32(g["repetition"])), where
+            assert list(e.masked) == g["mask"], where
+            assert e.logprobs_k == g["logprobs_k"], where
+            records.append(TokenLogprob(sampled[i], -0.5 * (i + 1), []) if e.logprobs_k >= 0
+                           else None)
+        deltas = sched.commit_step(sampled, records) if planned else []
+        done += sched.take_completed()
+        assert [[d.id, d.token, d.finish or "not_finished", d.logprob is not None]
+                for d in deltas] == rec["deltas"], f"step {step}: the tokens handed out differ"
+        assert sorted([c.id, c.reason, len(c.output_tokens)] for c in done) == \
+            sorted(rec["completed"]), f"step {step}: what finished differs"
+        assert (len(sched.running), len(sched.waiting), sched.preemptions) == \
+            (rec["running"], rec["waiting"], rec["preemptions"]), f"step {step}"
+        assert cache.pools[0].free_count == rec["free_blocks"], f"step {step}: free pages differ"
+        cache.check_invariants()
+    assert not sched.has_work()
+
+
+def test_plain_penalties_and_logprobs_against_the_reference_host_sampler():
+    """plain.penalised, plain.greedy and plain.logprobs (what the engine's sampling tests
+    compare the kernels with) against the reference's HostSampleRow on nine rows: changed
+    logits, the greedy choice with ties, the log-probability and the alternatives."""
+    import math
+    for rec in _records("sampling_golden.jsonl"):
+        r, vocab = rec["row"], rec["vocab"]
+        v = torch.arange(vocab, dtype=torch.float32)
+        row = 4.0 * torch.sin(0.37 * v + 1.3 * r) + 2.0 * torch.cos(0.11 * v * r + 0.5)
+        row[18] = row[17]
+        row[120] = row[121] = row[44]
+        generated = []
+        for t, c in rec["history"]:
+            if 0 <= t < vocab:
+                generated += [t] * c
+        masked = [t for t in rec["mask"] if 0 <= t < vocab]
+        out = plain.penalised(row, generated, rec["presence"], rec["frequency"],
+                              rec["repetition"], masked)
+        changed = {t: x for t, x in rec["changed"]}
+        for t in range(vocab):
+            if t in changed:
+                want = changed[t]
+                if want <= -1e29:
+                    assert out[t] == float("-inf"), (r, t)
+                else:
+                    assert abs(float(out[t]) - want) <= 2e-5 * max(1.0, abs(want)), (r, t)
+            else:
+                # the formula's sin and cos may differ from the C library's in the last bit
+                assert float(out[t]) == float(row[t]), (r, t)
+        got = plain.greedy(out)
+        assert got == rec["chosen"] or abs(float(out[got] - out[rec["chosen"]])) <= 1e-5, r
+        if rec["has_logprob"]:
+            lp, top = plain.logprobs(out, rec["chosen"], max(rec["logprobs_k"], 0))
+            assert abs(lp - rec["logprob"]) <= 1e-4
+            assert len(top) == len(rec["top"])
+            for (t, x), (gt, gx) in zip(top, rec["top"]):
+                assert abs(x - gx) <= 1e-4
+                assert t == gt or abs(float(out[t] - out[gt])) <= 1e-5
+        else:
+            assert rec["logprobs_k"] < 0
