@@ -152,10 +152,11 @@ class Qwen2MoeConfig:
         return self.sliding_window if self.layer_types[i] == SLIDING else 0
 
     def settled_keys(self) -> dict:
-        """Keys whose value this engine had to derive by a rule of its own; whoever
-        writes a model folder from this configuration states them, so that every
-        reader of the folder runs the same layers the same way."""
-        return {"layer_types": list(self.layer_types)}
+        """Keys whose value this engine had to derive by a rule of its own, or whose
+        default differs between readers of this architecture's files; whoever writes a
+        model folder from this configuration states them, so that every reader of the
+        folder runs the same layers the same way."""
+        return {"layer_types": list(self.layer_types), "norm_topk_prob": self.norm_topk_prob}
 
     # ---- parsing ------------------------------------------------------------
     @classmethod
@@ -227,7 +228,9 @@ class Qwen2MoeConfig:
                 "moe_intermediate_size", r.integer("intermediate_size", 0)
             ),
             shared_expert_intermediate_size=r.integer("shared_expert_intermediate_size", 0),
-            norm_topk_prob=r.boolean("norm_topk_prob", False),
+            # absent means renormalise, as in the reference (src/model/config.cc:361-362);
+            # checkpoints of this architecture state the key, most of them as false
+            norm_topk_prob=r.boolean("norm_topk_prob", True),
             decoder_sparse_step=sparse_step,
             mlp_only_layers=mlp_only,
             use_sliding_window=r.boolean("use_sliding_window", False),

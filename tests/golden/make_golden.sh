@@ -1,9 +1,10 @@
 #!/bin/sh
-# Compiles the reference's own scheduler, block pool and host sampler (unmodified sources of
+# Compiles the reference's own scheduler, block pool, host sampler and configuration parser
+# (unmodified sources of
 # a divedb/InferX checkout given as $1) on the CPU, against the small stand-in for abseil in
-# absl_stub/, links them with the two drivers of this folder and writes what they print to
-# scheduler_golden.jsonl and sampling_golden.jsonl.  tests/test_scheduler_golden.py reads
-# those two files; it needs neither the checkout nor a compiler.
+# absl_stub/, links them with the three drivers of this folder and writes what they print to
+# scheduler_golden.jsonl, sampling_golden.jsonl and config_golden.jsonl.  tests/test_scheduler_golden.py reads
+# those files; it needs neither the checkout nor a compiler.
 #
 #   sh tests/golden/make_golden.sh /path/to/InferX
 set -e
@@ -15,15 +16,19 @@ n=0
 for f in src/scheduler/scheduler.cc src/scheduler/prefix_cache.cc src/core/kv_cache.cc \
          src/core/device_buffer.cc src/core/tensor_view.cc src/core/shape.cc \
          src/core/device_runtime.cc src/backends/cpu/device_runtime.cc \
-         src/core/accelerator_runtime_stub.cc src/engine/host_sampling.cc; do
+         src/core/accelerator_runtime_stub.cc src/engine/host_sampling.cc \
+         src/model/config.cc src/support/json.cc; do
   n=$((n + 1))
   g++ -std=c++20 -O1 $INC -c "$REF/$f" -o "$OUT/ref_$n.o"
 done
 g++ -std=c++20 -O1 $INC -c "$HERE/scheduler_golden.cc" -o "$OUT/scheduler_golden.o"
 g++ -std=c++20 -O1 $INC -c "$HERE/sampling_golden.cc" -o "$OUT/sampling_golden.o"
+g++ -std=c++20 -O1 $INC -c "$HERE/config_golden.cc" -o "$OUT/config_golden.o"
 g++ "$OUT"/ref_*.o "$OUT/scheduler_golden.o" -o "$OUT/scheduler_golden"
 g++ "$OUT"/ref_*.o "$OUT/sampling_golden.o" -o "$OUT/sampling_golden"
+g++ "$OUT"/ref_*.o "$OUT/config_golden.o" -o "$OUT/config_golden"
 "$OUT/scheduler_golden" > "$HERE/scheduler_golden.jsonl"
 "$OUT/sampling_golden" > "$HERE/sampling_golden.jsonl"
-wc -l "$HERE/scheduler_golden.jsonl" "$HERE/sampling_golden.jsonl"
+"$OUT/config_golden" "$HERE"/config_cases/*.json > "$HERE/config_golden.jsonl"
+wc -l "$HERE/scheduler_golden.jsonl" "$HERE/sampling_golden.jsonl" "$HERE/config_golden.jsonl"
 rm -r "$OUT"

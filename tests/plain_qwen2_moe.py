@@ -212,7 +212,8 @@ def moe_block(cfg, w, prefix, x, rf=_identity):
     expert moe.cu:275-287).  Every expert is evaluated on its tokens only."""
     E, k = cfg["num_experts"], cfg["num_experts_per_tok"]
     logits = x @ w[f"{prefix}.gate.weight"].T
-    weights, experts = route(logits, k, cfg.get("norm_topk_prob", False))
+    # absent means renormalise (src/model/config.cc:361-362)
+    weights, experts = route(logits, k, cfg.get("norm_topk_prob", True))
     out = torch.zeros_like(x)
     for t in range(x.shape[0]):
         acc = torch.zeros(x.shape[1])

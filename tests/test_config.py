@@ -118,6 +118,24 @@ def test_attention_bias_spellings_and_eos(tiny_a):
         config_from_json(dict(tiny_a, eos_token_id="7"))
 
 
+def test_defaults_of_absent_keys_follow_the_reference(tiny_a):
+    """What config.json may leave out, and what that means (src/model/config.cc:353-365,
+    419-431): renormalised top-k weights, Q/K/V biases present, no shared expert, plain
+    head, no window."""
+    lean = {k: v for k, v in tiny_a.items()
+            if k not in ("norm_topk_prob", "attention_bias", "qkv_bias",
+                         "shared_expert_intermediate_size", "tie_word_embeddings",
+                         "use_sliding_window", "sliding_window", "max_window_layers",
+                         "layer_types")}
+    cfg = config_from_json(lean)[0]
+    assert cfg.norm_topk_prob is True
+    assert cfg.attention_bias is True
+    assert cfg.shared_expert_intermediate_size == 0
+    assert cfg.tie_word_embeddings is False
+    assert all(cfg.layer_window(i) == 0 for i in range(cfg.num_hidden_layers))
+    assert config_from_json(dict(lean, norm_topk_prob=False))[0].norm_topk_prob is False
+
+
 def test_from_dir_and_duplicate_keys(tmp_path, tiny_b):
     (tmp_path / "config.json").write_text(json.dumps(tiny_b))
     cfg, _ = config_from_dir(str(tmp_path))

@@ -147,3 +147,59 @@ def test_plain_penalties_and_logprobs_against_the_reference_host_sampler():
                 assert t == gt or abs(float(out[t] - out[gt])) <= 1e-5
         else:
             assert rec["logprobs_k"] < 0
+
+
+def test_typed_configuration_against_the_reference_parser():
+    """The keys of config.json as the reference's own parser read them
+    (tests/golden/config_golden.cc over tests/golden/config_cases/*.json), against this
+    repository's typed configuration: the same values key by key, except where the two
+    differ on purpose, each named here with its reason."""
+    from inferx_b200.config import ConfigError, config_from_json
+    same = ["hidden_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads",
+            "head_dim", "vocab_size", "rms_norm_eps", "rope_theta", "tie_word_embeddings",
+            "num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob",
+            "shared_expert_intermediate_size", "max_position_embeddings", "sliding_window"]
+    seen = set()
+    for rec in _records("config_golden.jsonl"):
+        name = rec["case"]
+        seen.add(name)
+        with open(os.path.join(HERE, "config_cases", name + ".json")) as f:
+            text = json.load(f)
+        if not rec["ok"]:
+            # the reference wants 'intermediate_size' always; here a model whose layers are
+            # all mixtures needs none (no tensor has that size), and says so when a dense
+            # layer does need it
+            assert name == "tiny_a" and "intermediate_size" in rec["error"]
+            cfg = config_from_json(text)[0]
+            assert all(cfg.layer_is_sparse(i) for i in range(cfg.num_hidden_layers))
+            with pytest.raises(ConfigError, match="intermediate_size"):
+                config_from_json(dict(text, mlp_only_layers=[0]))
+            continue
+        assert rec["architecture"] == "Qwen2MoeForCausalLM"
+        cfg = config_from_json(text)[0]
+        for key in same:
+            assert getattr(cfg, key) == rec[key], (name, key)
+        assert rec["routed_scaling_factor"] == 1.0        # not a key of this architecture
+        # Q/K/V biases: the reference assumes them for its dense Qwen2 only and reads none for
+        # this architecture, whose checkpoints it cannot load anyway; the architecture has
+        # them, so absent means present here (the loader checks the flag against the tensors)
+        if "attention_bias" in text:
+            assert cfg.attention_bias == rec["attention_bias"] == text["attention_bias"]
+        else:
+            assert cfg.attention_bias is True and rec["attention_bias"] is False
+        # which layers are mixtures: the reference knows DeepSeek's keys only and calls
+        # every layer one; 'decoder_sparse_step' and 'mlp_only_layers' are this
+        # architecture's own, and both agree where those leave every layer a mixture
+        assert all(rec["moe_layers"])
+        if text.get("decoder_sparse_step", 1) == 1 and not text.get("mlp_only_layers"):
+            assert all(cfg.layer_is_sparse(i) for i in range(cfg.num_hidden_layers)), name
+        # which layers slide: the reference reads 'layer_types' and nothing else; so does
+        # this build when the list is there (and 'use_sliding_window' is on), and derives
+        # it from 'max_window_layers' when it is not
+        slides = [cfg.layer_window(i) > 0 for i in range(cfg.num_hidden_layers)]
+        if "layer_types" in text:
+            assert text.get("use_sliding_window") and slides == rec["layer_is_sliding"], name
+        else:
+            assert rec["layer_is_sliding"] == []
+    assert seen == {"full", "lean", "tiny_a", "tiny_b", "tiny_b_listed", "bias_off", "bias_on",
+                    "tied_gqa_headdim"}
