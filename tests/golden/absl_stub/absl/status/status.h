@@ -24,6 +24,7 @@ class Status {
   StatusCode code() const { return code_; }
   const std::string& message() const { return message_; }
   std::string ToString() const { return ok() ? "OK" : message_; }
+  void IgnoreError() const {}
   friend bool operator==(const Status& a, const Status& b) {
     return a.code_ == b.code_ && a.message_ == b.message_;
   }

@@ -203,3 +203,31 @@ def test_typed_configuration_against_the_reference_parser():
             assert rec["layer_is_sliding"] == []
     assert seen == {"full", "lean", "tiny_a", "tiny_b", "tiny_b_listed", "bias_off", "bias_on",
                     "tied_gqa_headdim"}
+
+
+def test_written_model_folder_is_what_the_reference_reader_reads(tmp_path):
+    """tests/golden/checkpoint_golden.jsonl is what the reference's own safetensors reader
+    found in the folder that `write_random_model` wrote for config_cases/tiny_b.json with
+    seed 7: every tensor's name, element type, shape and a hash of its bytes.  Written
+    again now and read with this repository's reader it is the same: the writer's file is
+    valid for the reference, both readers see the same bytes, and seeded weights do not
+    change from one day to the next."""
+    from inferx_b200.weights.random_model import write_random_model
+    from inferx_b200.weights.safetensors_io import Checkpoint
+    with open(os.path.join(HERE, "config_cases", "tiny_b.json")) as f:
+        cfg = json.load(f)
+    d = str(tmp_path / "m")
+    write_random_model(cfg, d, seed=7, dtype="bfloat16")
+    ck = Checkpoint(d)
+    golden = _records("checkpoint_golden.jsonl")
+    assert sorted(ck.names()) == [g["name"] for g in golden] and len(golden) == 64
+    names = {torch.bfloat16: "bf16", torch.float32: "f32", torch.int32: "i32"}
+    for g in golden:
+        e = ck.entry(g["name"])
+        assert (names[e.dtype], list(e.shape), e.end - e.begin) == \
+            (g["dtype"], g["shape"], g["nbytes"]), g["name"]
+        h = 1469598103934665603
+        for b in ck.get(g["name"]).contiguous().view(torch.uint8).reshape(-1).tolist():
+            h = ((h ^ b) * 1099511628211) & ((1 << 64) - 1)
+        assert f"{h:016x}" == g["fnv1a"], g["name"]
+    ck.close()
