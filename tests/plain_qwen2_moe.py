@@ -6,8 +6,10 @@ which cannot be compiled or imported on the CPU here (its ``third_party/`` is
 empty), so there is no golden output of the forward pass made by the reference itself
 (its scheduler and its host sampler do compile on the CPU: tests/golden/ holds what they
 decide, and tests/test_scheduler_golden.py compares this file's sampling statements and
-the package's scheduler with that).  Each function below cites the reference lines whose
-arithmetic it restates.  It shares no code
+the package's scheduler with that; its CUDA kernels compile too, tests/golden/ops_golden.bin
+holds what they computed on a B200 for every part below, and tests/test_ops_golden.py
+compares the functions of this file with that).  Each function below cites the reference
+lines whose arithmetic it restates.  It shares no code
 with ``inferx_b200``: it reads config.json as a plain dict and the tensors by
 their checkpoint names from a plain dict of fp32 CPU tensors.
 
