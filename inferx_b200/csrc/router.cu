@@ -151,8 +151,15 @@ __device__ __forceinline__ void dot8(float& acc, const float* xf, const float4& 
 
 #define ROUTER_VTHREADS 512
 #define ROUTER_VROWS 4
+#define ROUTER_MANY_TOKENS 1024
+#define ROUTER_SMS 148   // B200; another count only shifts the choice, never the result
 
-template <int ROUTER_VTOK>
+// WIDE: the block's activations are widened to 32-bit once, when they are staged, and kept
+// as two planes of float4 (the first and the second half of every 8-element chunk, so that a
+// warp's 16-byte reads are contiguous); otherwise they stay bfloat16 in shared memory and are
+// widened at every use.  Widening is exact, so both give the same bits; the wide form issues
+// a fifth fewer instructions and is taken when its tile fits.
+template <int ROUTER_VTOK, bool WIDE>
 __global__ void __launch_bounds__(ROUTER_VTHREADS)
 router_topk_bf16_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ w,
                             const float* __restrict__ extra_w, int T, int H, int E, int k,
@@ -161,20 +168,32 @@ router_topk_bf16_vec_kernel(const bf16* __restrict__ x, const float* __restrict_
   extern __shared__ __align__(16) unsigned char rsm[];
   const int chunks = H >> 3;
   uint4* xs = reinterpret_cast<uint4*>(rsm);                               // [VTOK][chunks]
-  float* lg = reinterpret_cast<float*>(rsm + (size_t)ROUTER_VTOK * chunks * 16);   // [VTOK][E]
+  float4* xlo = reinterpret_cast<float4*>(rsm);                            // [VTOK][chunks]
+  float4* xhi = xlo + (size_t)ROUTER_VTOK * chunks;                        // [VTOK][chunks]
+  float* lg = reinterpret_cast<float*>(
+      rsm + (size_t)ROUTER_VTOK * chunks * (WIDE ? 32 : 16));              // [VTOK][E]
   const int t0 = blockIdx.x * ROUTER_VTOK;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nwarps = ROUTER_VTHREADS / 32;
   for (int idx = threadIdx.x; idx < ROUTER_VTOK * chunks; idx += ROUTER_VTHREADS) {
     const int tk = idx / chunks, c = idx - tk * chunks;
     const int t = t0 + tk;
-    xs[idx] = t < T ? reinterpret_cast<const uint4*>(x + (size_t)t * H)[c] : make_uint4(0, 0, 0, 0);
+    const uint4 raw =
+        t < T ? reinterpret_cast<const uint4*>(x + (size_t)t * H)[c] : make_uint4(0, 0, 0, 0);
+    if (WIDE) {
+      float xf[8];
+      bf8_to_f32(raw, xf);
+      xlo[idx] = make_float4(xf[0], xf[1], xf[2], xf[3]);
+      xhi[idx] = make_float4(xf[4], xf[5], xf[6], xf[7]);
+    } else {
+      xs[idx] = raw;
+    }
   }
   __syncthreads();
   const int rows_total = E + (extra_w ? 1 : 0);
   // A warp takes ROUTER_VROWS weight rows at a time, so that a chunk of activations
-  // read from shared memory and widened once feeds that many dot products (one row at
-  // a time the loop is bound by shared-memory reads, not by the multiply-adds).
+  // read from shared memory feeds that many dot products (one row at a time the loop is
+  // bound by shared-memory reads, not by the multiply-adds).
   for (int e0 = warp * ROUTER_VROWS; e0 < rows_total; e0 += nwarps * ROUTER_VROWS) {
     const float4* wr[ROUTER_VROWS];
 #pragma unroll
@@ -197,7 +216,13 @@ router_topk_bf16_vec_kernel(const bf16* __restrict__ x, const float* __restrict_
 #pragma unroll
       for (int tk = 0; tk < ROUTER_VTOK; ++tk) {
         float xf[8];
-        bf8_to_f32(xs[tk * chunks + c], xf);
+        if (WIDE) {
+          const float4 lo = xlo[tk * chunks + c], hi = xhi[tk * chunks + c];
+          xf[0] = lo.x; xf[1] = lo.y; xf[2] = lo.z; xf[3] = lo.w;
+          xf[4] = hi.x; xf[5] = hi.y; xf[6] = hi.z; xf[7] = hi.w;
+        } else {
+          bf8_to_f32(xs[tk * chunks + c], xf);
+        }
 #pragma unroll
         for (int r = 0; r < ROUTER_VROWS; ++r) dot8(acc[tk][r], xf, wa[r], wb[r]);
       }
@@ -221,6 +246,22 @@ router_topk_bf16_vec_kernel(const bf16* __restrict__ x, const float* __restrict_
     select_topk(lg + tk * E, E, k, renorm, scale, topk_w + (size_t)t * k, topk_idx + (size_t)t * k,
                 lane);
   }
+}
+
+template <int VTOK, bool WIDE>
+static int launch_router_vec(const void* x, const float* w, const float* extra_w, int T, int H,
+                             int E, int k, int renorm, float scale, float* topk_w, int* topk_idx,
+                             float* extra_out, cudaStream_t stream) {
+  const size_t smem = (size_t)VTOK * (H / 8) * (WIDE ? 32 : 16) + (size_t)VTOK * E * sizeof(float);
+  auto kern = router_topk_bf16_vec_kernel<VTOK, WIDE>;
+  if (smem > 48 * 1024) {
+    cudaError_t e2 =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e2 != cudaSuccess) return (int)e2;
+  }
+  kern<<<(T + VTOK - 1) / VTOK, ROUTER_VTHREADS, smem, stream>>>(
+      (const bf16*)x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx, extra_out);
+  return ix_launch_status();
 }
 
 __global__ void __launch_bounds__(ROUTER_THREADS)
@@ -324,22 +365,40 @@ IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, i
     return ix_launch_status();
   }
   if (vec) {
-    // 16 tokens share one pass over the router weights when there are enough tokens;
-    // fewer tokens per block otherwise (measured crossover at 60 experts of 2048: the
-    // 16-token form takes 29 us up to 2048 tokens, the 4-token form 19 us at 1024 tokens
-    // and 30 us at 1536)
-    const int vtok = T >= 1408 ? 16 : 4;
-    const size_t smem = (size_t)vtok * (H / 8) * 16 + (size_t)vtok * E * sizeof(float);
-    if (smem <= 200 * 1024) {
-      auto kern = vtok == 16 ? router_topk_bf16_vec_kernel<16> : router_topk_bf16_vec_kernel<4>;
-      if (smem > 48 * 1024) {
-        cudaError_t e2 =
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e2 != cudaSuccess) return (int)e2;
+    // Tokens of a block share one pass over the router weights.  A block takes 4 tokens
+    // while there are few.  From ROUTER_MANY_TOKENS on it takes 8 to 16: a block of v tokens
+    // costs about 6.5 + 1.4 v microseconds at 60 experts of 2048 however many blocks run
+    // beside it, one block fits an SM, and so the count is chosen for which the rounds of
+    // blocks an SM sees cost least (2048 tokens: 14 a block is 147 blocks, one round on 147
+    // SMs, 26.8 us; 16 a block leaves 20 SMs idle, 29.5 us; 4096 tokens: 51.5 against 56.7).
+    int vtok = 4;
+    if (T >= ROUTER_MANY_TOKENS) {
+      float best = -1.f;
+      for (int v = 16; v >= 8; v -= 2) {
+        const long long blocks = (T + v - 1) / v;
+        const float cost = (float)((blocks + ROUTER_SMS - 1) / ROUTER_SMS) * (6.5f + 1.4f * v);
+        if (best < 0.f || cost < best) { best = cost; vtok = v; }
       }
-      kern<<<(T + vtok - 1) / vtok, ROUTER_VTHREADS, smem, stream>>>(
-          (const bf16*)x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx, extra_out);
-      return ix_launch_status();
+    }
+    const size_t lg_bytes = (size_t)vtok * E * sizeof(float);
+    // widened staging pays from 10 tokens a block on (a few tenths of a microsecond)
+    const bool wide = vtok >= 10 && (size_t)vtok * H * 4 + lg_bytes <= 200 * 1024;
+    if ((size_t)vtok * H * 2 + lg_bytes <= 200 * 1024) {
+#define IX_ROUTER_CASE(V)                                                                       \
+  case V:                                                                                       \
+    return wide ? launch_router_vec<V, true>(x, w, extra_w, T, H, E, k, renorm, scale, topk_w,  \
+                                             topk_idx, extra_out, stream)                       \
+                : launch_router_vec<V, false>(x, w, extra_w, T, H, E, k, renorm, scale, topk_w, \
+                                              topk_idx, extra_out, stream);
+      switch (vtok) {
+        IX_ROUTER_CASE(4)
+        IX_ROUTER_CASE(8)
+        IX_ROUTER_CASE(10)
+        IX_ROUTER_CASE(12)
+        IX_ROUTER_CASE(14)
+        IX_ROUTER_CASE(16)
+      }
+#undef IX_ROUTER_CASE
     }
   }
   // many tokens share one pass over the router weights; few tokens spread out

@@ -451,7 +451,7 @@ def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, renormalize: bool,
 
     Returns (weights [T,k] fp32, experts [T,k] int32, x.extra_w [T] fp32 or None).
     Few tokens: one warp per (token, expert) computes the logits and one warp per
-    token selects; many tokens: one fused kernel over 16 tokens per block.  Both form
+    token selects; many tokens: one fused kernel over 4 to 16 tokens per block.  Both form
     a dot product in the same order, so a token's routing is the same in either."""
     _chk("x", x)
     _chk("w", w, torch.float32)
