@@ -301,6 +301,41 @@ def time_prefill(rt, tokens, reps, warmup):
     return times[len(times) // 2]
 
 
+def time_prefill_sustained(rt, tokens, seconds):
+    """Prompt steps back to back for ``seconds``: a prompt step draws enough power for the
+    part to reach its power limit within a second or two, the clock sinks, and the step
+    takes longer than the first few did.  Returns the median of the last third of the steps
+    with the clock and the throttle reasons sampled during that third."""
+    import torch
+    from inferx_b200.engine import StepEntry
+    mgr = rt.manager
+    g = torch.Generator().manual_seed(7)
+    toks = torch.randint(0, rt.vocab_size, (tokens,), generator=g).tolist()
+    clock = ClockSampler()
+    clock.start()
+    times, stamps = [], []
+    t_end = time.perf_counter() + seconds
+    while time.perf_counter() < t_end:
+        for rid in list(mgr.live_requests()):
+            mgr.close(rid)
+        mgr.open("p")
+        assert mgr.reserve("p", tokens)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        rt.executor.step([StepEntry("p", toks, [tokens - 1])])
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+        stamps.append(time.perf_counter())
+    mgr.close("p")
+    last = max(1, len(times) // 3)
+    clock.t_begin = stamps[-last]
+    seen = clock.stop()
+    tail = sorted(times[-last:])
+    return {"ms": tail[len(tail) // 2], "steps": len(times), "sm_mhz": seen["sm_mhz"],
+            "reasons": "+".join(seen["reasons"]) or "none"}
+
+
 def time_mixed(rt, batch, context, chunk, reps, warmup):
     """One step that carries a prompt portion of ``chunk`` tokens beside ``batch``
     decoding requests at ``context``: milliseconds a step (median)."""
@@ -485,17 +520,44 @@ def breakdown(rt, batch, context, steps, prefill_tokens=0):
     return "\n".join(lines)
 
 
-def marginal(rt, batch, context, steps):
-    """What each kernel face costs *inside* the recorded step: the decode step is timed
-    again with that face's launches left out (it hands back the result of its first
-    call), and the difference is what the face adds to the step where it runs, with
-    dependent launch, the side stream and its neighbours as they are.  A diagnostic, not a
-    bench value: the steps it times compute nonsense."""
+def marginal(rt, batch, context, steps, prefill_tokens=0, qkv_rows=0):
+    """What each kernel face costs *inside* the recorded step: the decode step (or, with
+    ``prefill_tokens``, a prompt step of that many tokens) is timed again with that
+    face's launches left out (it hands back the result of its first call), and the
+    difference is what the face adds to the step where it runs, with dependent launch, the
+    side stream and its neighbours as they are.  A diagnostic, not a bench value: the
+    steps it times compute nonsense."""
     import torch
     from inferx_b200.engine.executor import GraphCache
     from inferx_b200.kernels import ops
 
+    # A prompt step draws enough power for the clock to sink while the list is measured
+    # (11.5 ms on a cool part, 12.8 ms forty steps later), which is more than most faces
+    # cost.  So the whole step is recorded once, every variant is recorded beside it, and
+    # the two recordings are replayed in turns: what is reported is the median of the
+    # differences between neighbours.
+    whole = {}
+
+    def record_prompt():
+        rt.executor._graphs = GraphCache()
+        time_prefill(rt, prefill_tokens, 1, 3)      # a prompt shape is recorded the third time
+        return rt.executor._graphs
+
     def run():
+        if prefill_tokens:
+            if "graphs" not in whole:
+                whole["graphs"] = record_prompt()
+                rt.executor._graphs = whole["graphs"]
+                return time_prefill(rt, prefill_tokens, 7, 0)
+            variant = record_prompt()
+            pairs = []
+            for _ in range(9):
+                rt.executor._graphs = whole["graphs"]
+                a = time_prefill(rt, prefill_tokens, 1, 0)
+                rt.executor._graphs = variant
+                pairs.append((a, time_prefill(rt, prefill_tokens, 1, 0)))
+            whole["base"] = sorted(a for a, _ in pairs)[len(pairs) // 2]
+            return whole["base"] - sorted(a - b for a, b in pairs)[len(pairs) // 2]
         rt.executor._graphs = GraphCache()       # the same shape must be recorded anew
         return time_decode(rt, batch, context, steps, 4)["ms_per_step"]
 
@@ -504,7 +566,9 @@ def marginal(rt, batch, context, steps):
     ops.grouped_down = lambda act, offsets, w, offsets_settled=False: settled(act, offsets, w)
     layers = rt.model.spec.schedule.__len__()
     base = run()
-    lines = [f"decode step, batch {batch}, context {context}: {base:.4f} ms",
+    what = (f"prompt step, {prefill_tokens} tokens" if prefill_tokens
+            else f"decode step, batch {batch}, context {context}")
+    lines = [f"{what}: {base:.4f} ms",
              f"{'left out':44s} {'ms/step':>9s} {'us/layer':>9s} {'us/step':>9s}"]
 
     def without(names, pred=None):
@@ -531,6 +595,11 @@ def marginal(rt, batch, context, steps):
     faces = [
         ("attention over the cache (+ merge)", ["paged_attention"], None),
         ("QKV product + rotation + cache write", ["qkv_project_rope_append"], None),
+        ("QKV product (library)", ["linear"],
+         lambda n, a: tuple(a[1].shape) == (qkv_rows, hidden) and qkv_rows != hidden),
+        ("rotation + cache write", ["qkv_rope_append"], None),
+        ("shared expert's SwiGLU", ["silu_mul"], None),
+        ("gather of the routed rows", ["gather_rows"], None),
         ("output projection", ["linear"], lambda n, a: tuple(a[1].shape) == (hidden, hidden)),
         ("vocabulary projection", ["linear"], lambda n, a: a[1].shape[0] == rt.vocab_size),
         ("routed gate/up + SwiGLU", ["grouped_gate_up_swiglu"], None),
@@ -545,6 +614,7 @@ def marginal(rt, batch, context, steps):
     try:
         for name, names, pred in faces:
             t = without(names, pred)
+            base = whole.get("base", base)       # a prompt step: the whole step timed beside it
             lines.append(f"{name:44s} {t:9.4f} {(base - t) * 1e3 / layers:9.1f} "
                          f"{(base - t) * 1e3:9.0f}")
     finally:
@@ -724,6 +794,8 @@ def main(argv=None):
                     help="print device time per kernel face instead of the bench line")
     ap.add_argument("--marginal", action="store_true",
                     help="print what each kernel face adds to the recorded decode step")
+    ap.add_argument("--prefill-tokens", type=int, default=0,
+                    help="with --marginal: a prompt step of this many tokens instead")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm()
@@ -779,7 +851,9 @@ def main(argv=None):
                       max_slots=max(B, big_b if points_wanted else B) + 1)
 
     if args.marginal:
-        print(marginal(rt, B, C, min(args.steps, 24)))
+        print(marginal(rt, B, C, min(args.steps, 24), prefill_tokens=args.prefill_tokens,
+                       qkv_rows=(cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"])
+                       * cfg["head_dim"]))
         return 0
     if args.breakdown:
         print(breakdown(rt, B, C, min(args.steps, 4),
@@ -835,6 +909,12 @@ def main(argv=None):
                           "ms": round(pms, 3),
                           "frac": round(fl / (pms / 1e3) / (tf_peak * 1e12), 4),
                           "flops": int(fl), "peak_tflops": tf_peak, "peak_source": peak_src}
+        sus = time_prefill_sustained(rt, 2048, 2.5)
+        points["prefill_2048_sustained_ms"] = round(sus["ms"], 3)
+        points["prefill_2048_sustained_frac"] = round(
+            fl / (sus["ms"] / 1e3) / (tf_peak * 1e12), 4)
+        points["prefill_2048_sustained_sm_mhz"] = sus["sm_mhz"]
+        points["prefill_2048_sustained_reasons"] = sus["reasons"]
         # further contexts and prompt lengths (what the cache pool of the widest run holds)
         for c in (16384, 32768):
             if B * (c + extra + 16) <= pool_tokens:

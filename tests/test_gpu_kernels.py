@@ -127,6 +127,46 @@ def test_qkv_rope_append(dtype, heads, kvh, hd, rot):
     assert torch.equal(kc2, kc_d) and torch.equal(vc2, vc_d)
 
 
+@pytest.mark.parametrize("heads,kvh,hd,rot", [(5, 5, 16, 16), (6, 2, 48, 48), (3, 1, 80, 32),
+                                              (4, 2, 128, 0), (16, 16, 128, 128)])
+def test_qkv_rope_append_many_tokens_same_bits(heads, kvh, hd, rot):
+    """The rows of a long step equal the same rows run in portions of 20, bit for bit, at
+    positions up to 40,000, and agree with the plain statement.  One token has no slot: its
+    keys and values go nowhere."""
+    ops = _ops()
+    dtype = torch.bfloat16
+    T, page = 150, 8
+    P = T // page + 2
+    width = (heads + 2 * kvh) * hd
+    qkv = _rand((T, width), dtype, seed=16)
+    bias = _rand((width,), torch.float32, 0.5, seed=17)
+    positions = (torch.arange(T, dtype=torch.int32) * 211) % 40000
+    inv = (10000.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / max(rot, 1))).float()
+    slots = torch.randperm(P * page)[:T].to(torch.int32)
+    slots[77] = -1
+    kc = torch.zeros(P, kvh, page, hd, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    inv_d = inv.cuda() if rot else None
+    kc_d, vc_d = kc.clone().cuda(), vc.clone().cuda()
+    q, k, v = ops.qkv_rope_append(qkv.cuda(), bias.cuda(), positions.cuda(), inv_d, rot, heads,
+                                  kvh, hd, kc_d, vc_d, slots.cuda(), want_dense_kv=True)
+    kc_p, vc_p = kc.clone().cuda(), vc.clone().cuda()
+    for lo in range(0, T, 20):
+        hi = min(T, lo + 20)
+        q2, k2, v2 = ops.qkv_rope_append(qkv[lo:hi].contiguous().cuda(), bias.cuda(),
+                                         positions[lo:hi].contiguous().cuda(), inv_d, rot, heads,
+                                         kvh, hd, kc_p, vc_p, slots[lo:hi].contiguous().cuda(),
+                                         want_dense_kv=True)
+        assert torch.equal(q[lo:hi], q2) and torch.equal(k[lo:hi], k2) and torch.equal(v[lo:hi], v2)
+    assert torch.equal(kc_d, kc_p) and torch.equal(vc_d, vc_p)
+    qr, kr, vr = host_ops.qkv_rope_append(qkv, bias, positions, inv if rot else None, rot, heads,
+                                          kvh, hd, kc, vc, slots, want_dense_kv=True)
+    _close(q.cpu(), qr, dtype)
+    _close(k.cpu(), kr, dtype)
+    _close(kc_d.cpu(), kc, dtype)
+    _close(vc_d.cpu(), vc, dtype)
+
+
 def _paged_case(dtype, heads, kvh, hd, page, window, seq_lens, q_lens, seed=0):
     """Random paged caches with shuffled pages; queries are the last q_len positions."""
     g = torch.Generator().manual_seed(seed)
