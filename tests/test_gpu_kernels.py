@@ -542,7 +542,7 @@ def test_small_m_dense(M, N, K):
 
 
 @pytest.mark.parametrize("T,H", [(600, 256), (1024, 256), (1412, 136), (2050, 136), (1800, 4096),
-                                 (1180, 4096)])
+                                 (1180, 4096), (2048, 2048)])
 def test_router_paths_agree_bitwise(T, H):
     """Few tokens take the two-kernel router, many the fused one with 4 to 16 tokens a block
     (1024 tokens: 8 a block; 1412: 10; 1800: 14, 1180: 8, and at a width of 4096 the tile of
